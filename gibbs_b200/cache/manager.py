@@ -4,15 +4,15 @@ Two kinds of memory, both sized once at start:
 
 * **Pages** for mixers that keep keys and values per position.  Entries of the
   model's order with the same retention rule form a *group* (all keys; the
-  last ``window`` keys).  A group has a pool of page ids of its own and every
+  last ``window`` keys; the keys of the current block of ``block`` positions).  A group has a pool of page ids of its own and every
   request has one block table per group; a page id addresses the same page in
   the key and value tensors of every entry of the group
   (``[n_pages, kv_heads, page_size, head_dim]`` each), and in the row tensors
   (``[n_pages, page_size, width]``) of entries that keep one plain row per
   position (``PagedRows``).  Pages are taken as a
-  request grows, given back when it ends, and in a windowed group also as
-  soon as the window has passed them; the ids are then reused by whoever asks
-  next.
+  request grows, given back when it ends, and in a windowed or blocked group
+  also as soon as the window (the block) has passed them; the ids are then
+  reused by whoever asks next.
 * **Slots** for per-request state of fixed size (a short convolution's last
   inputs, a recurrent state).  One slot holds the state of every entry that
   needs some, as byte ranges of one row; a slot is zeroed when a request
@@ -49,6 +49,7 @@ class PagedKVView:
     page_size: int
     writable: bool
     window: Optional[int]
+    block: Optional[int] = None        # the pages keep the current block of this many positions
 
 
 @dataclass
@@ -72,6 +73,7 @@ class SlotView:
 class _Group:
     window: Optional[int]
     pool: IdPool
+    block: Optional[int] = None                     # positions seen in blocks of this many instead of a window
     entries: list = field(default_factory=list)     # (entry index, need index)
 
 
@@ -91,7 +93,8 @@ class CacheManager:
                  max_context: int, guard: bool = False):
         """entry_needs: for each entry of the model's order, (list of needs,
         entry whose cache it reads instead or None).  n_pages: an int (for
-        every group) or a dict from window (None = all keys) to a count.
+        every group) or a dict from retention rule (None = all keys, a window
+        length, ("block", size)) to a count.
         ``guard``: one page before and after every page tensor, one slot row
         before and after the slots and 16 bytes behind every slot are filled
         with a pattern that ``check`` looks at: a kernel that writes outside
@@ -110,17 +113,19 @@ class CacheManager:
         self._pages: dict[tuple[int, int], tuple[torch.Tensor, torch.Tensor]] = {}
         self._slot_ranges: dict[tuple[int, int], tuple[int, int, SlotState]] = {}
         slot_bytes = 0
-        by_window: dict[Optional[int], int] = {}
+        by_window: dict = {}
         for e, (needs, reads) in enumerate(entry_needs):
             if reads is not None:
                 continue
             for k, need in enumerate(needs):
                 if isinstance(need, (PagedKV, PagedRows)):
-                    if need.window not in by_window:
-                        count = n_pages[need.window] if isinstance(n_pages, dict) else n_pages
-                        by_window[need.window] = len(self.groups)
-                        self.groups.append(_Group(need.window, IdPool(count, "page")))
-                    g = by_window[need.window]
+                    rule = need.retention
+                    if rule not in by_window:
+                        count = n_pages[rule] if isinstance(n_pages, dict) else n_pages
+                        by_window[rule] = len(self.groups)
+                        self.groups.append(_Group(need.window, IdPool(count, "page"),
+                                                  block=getattr(need, "block", None)))
+                    g = by_window[rule]
                     self.groups[g].entries.append((e, k))
                     self._group_of[(e, k)] = g
                     if isinstance(need, PagedRows):
@@ -206,6 +211,8 @@ class CacheManager:
     def _first_needed_page(self, group: _Group, start_pos: int) -> int:
         """Index (in the block table) of the first page a step that starts at
         start_pos can still read."""
+        if group.block is not None:
+            return (start_pos // group.block) * group.block // self.page_size
         if group.window is None:
             return 0
         return max(0, start_pos - group.window + 1) // self.page_size
@@ -337,7 +344,7 @@ class CacheManager:
                 elif isinstance(need, PagedKV):
                     kp, vp = self._pages[(owner, k)]
                     g = self._group_of[(owner, k)]
-                    views.append(PagedKVView(kp, vp, block_tables[g], self.page_size, reads is None, need.window))
+                    views.append(PagedKVView(kp, vp, block_tables[g], self.page_size, reads is None, need.window, need.block))
                 else:
                     views.append(SlotView(self._slot_views[(owner, k)], slot_ids, host_slot_ids))
             out.append(views)

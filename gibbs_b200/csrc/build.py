@@ -29,9 +29,10 @@ LIBRARIES = {
     "core": ["errors.cu", "elementwise.cu", "gemm_simt.cu", "conv.cu", "attention.cu", "sampling.cu"],
     "tensorcore": ["errors.cu", "gemm_tc.cu", "gemm_tc_decode.cu", "attention_tc.cu", "attention_tcgen05.cu"],
     "runtime": ["errors.cu", "step_plan.cu"],
-    # layer norms, clamped gated units, latent and gated attention, state-space recurrences, routed experts: every entry
+    # layer norms, clamped gated units, latent and gated attention, state-space and delta-rule recurrences, routed experts: every entry
     # point has the signature of a step-plan operation (hybrid.cuh)
-    "hybrid": ["errors.cu", "norms.cu", "latent_attention.cu", "gated_attention.cu", "gated_attention_tc.cu", "ssm.cu", "moe.cu", "moe_tc.cu"],
+    "hybrid": ["errors.cu", "norms.cu", "latent_attention.cu", "gated_attention.cu", "gated_attention_tc.cu", "ssm.cu", "delta_rule.cu",
+               "moe.cu", "moe_tc.cu"],
 }
 
 NVCC_FLAGS = [

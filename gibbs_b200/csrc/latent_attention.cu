@@ -10,7 +10,8 @@
 //                          token's page; rotation of the queries' rotated parts into q'
 //  gb_op_head_linear       out[t, h, :] = x[t, h, :] W[h]^T for every head (absorbing W_uk, applying W_uv)
 //  gb_op_latent_attention  softmax(scale * q' . rows) over the last `window` rows (all when 0), times the
-//                          rows' latent part, times sigmoid(gate[t, h]); scores and weights in 32-bit
+//                          rows' latent part, times sigmoid(gate[t, h]) where there is a gate; with a sink,
+//                          exp(sink[h]) is added to the softmax's denominator; scores and weights in 32-bit
 //
 // Rotation: the first `rot_dims` entries of a rotated part turn in adjacent pairs (2i, 2i+1) by
 // pos * inv_freq[i] (angle in 32-bit); the rest passes unchanged.
@@ -189,7 +190,7 @@ __global__ void __launch_bounds__(32 * LA_WARPS, 2)      // (two blocks an SM: a
 latent_attention_kernel(const float* qp, const TC* pages, const int* block_table, int bt_stride, int page_size,
                         int n_pages, const int* tok_req, const int* tok_pos, const float* gate, long long ld_gate,
                         float* out, long long ldo, int H, int r, int dr, float scale, int window, int splits, int chunk,
-                        float* ws, int* status) {
+                        float* ws, const float* __restrict__ sink, int* status) {
   extern __shared__ __align__(16) float ks[];      // [LA_KT][Dk]
   pdl_trigger();
   const int Dk = r + dr;
@@ -310,19 +311,27 @@ latent_attention_kernel(const float* qp, const TC* pages, const int* block_table
       continue;
     }
     const float g = gate ? hy_sigmoid(gate[(size_t)t * ld_gate + h]) : 1.f;
-    const float inv = g / l[hh];
+    float inv = g / l[hh], e = 1.f;
+    if (sink) {
+      // a learned score without a key or a value: it only joins the denominator (by the merge kernel's
+      // arithmetic, so that one chunk and several of which one holds keys give the same bits)
+      const float top = fmaxf(m[hh], sink[h]);
+      e = expf(m[hh] - top);
+      inv = g / __fadd_rn(expf(sink[h] - top), __fmul_rn(e, l[hh]));
+    }
     float* o = out + (size_t)t * ldo + (size_t)h * r;
 #pragma unroll
     for (int i = 0; i < RL; ++i) {
       const int d = lane + 32 * i;
-      if (d < r) o[d] = acc[hh][i] * inv;
+      if (d < r) o[d] = __fmul_rn(e, acc[hh][i]) * inv;
     }
   }
 }
 
 // One warp per (token, head): the chunks' partial results, merged in chunk order.
 __global__ void latent_attention_merge_kernel(const float* ws, int splits, const float* gate, long long ld_gate,
-                                              float* out, long long ldo, int n, int H, int r) {
+                                              float* out, long long ldo, int n, int H, int r,
+                                              const float* __restrict__ sink) {
   pdl_trigger();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -334,7 +343,8 @@ __global__ void latent_attention_merge_kernel(const float* ws, int splits, const
   float M = -INFINITY;
   for (int s = lane; s < splits; s += 32) M = fmaxf(M, w[(size_t)s * (r + 2)]);
   M = warp_max(M);
-  float L = 0.f;
+  if (sink) M = fmaxf(M, sink[h]);
+  float L = sink ? expf(sink[h] - M) : 0.f;
   for (int s0 = 0; s0 < splits; s0 += 32) {                // in chunk order
     const int s = s0 + lane;
     const float m = s < splits ? w[(size_t)s * (r + 2)] : -INFINITY;
@@ -443,7 +453,8 @@ GB_OP(gb_op_head_linear) {
 // size, a6 number of pages, a7 token -> request, a8 token -> position, a9 gate logits (f32, [t, h] at a row stride) or
 // 0, a10 that stride, a11 out [tokens, heads * r] (f32), a12 its row stride, a13 tokens, a14 heads, a15 latent size,
 // a16 rotated size, a17 window (0: every earlier position), a18 longest context of the step (an upper bound will do),
-// a19 workspace for partial results, gb_latent_attention_workspace_rows() rows of (latent size + 2) floats; f0 scale
+// a19 workspace for partial results, gb_latent_attention_workspace_rows() rows of (latent size + 2) floats, a20 a
+// learned sink score per head (f32 [heads]) whose exponential joins the softmax's denominator, or 0; f0 scale
 GB_OP(gb_op_latent_attention) {
   const int n = (int)a[13], H = (int)a[14], r = (int)a[15], dr = (int)a[16];
   if (n <= 0) return 0;
@@ -468,7 +479,7 @@ GB_OP(gb_op_latent_attention) {
     gb_launch(latent_attention_kernel<TC, RL>, grid, block, smem, ctx->stream, op_ptr<const float>(a[0]),             \
               op_ptr<const TC>(a[1]), op_ptr<const int>(a[3]), (int)a[4], (int)a[5], (int)a[6], op_ptr<const int>(a[7]), \
               op_ptr<const int>(a[8]), op_ptr<const float>(a[9]), a[10], op_ptr<float>(a[11]), a[12], H, r, dr,       \
-              (float)f[0], (int)a[17], splits, chunk, ws, ctx->status);                                              \
+              (float)f[0], (int)a[17], splits, chunk, ws, op_ptr<const float>(a[20]), ctx->status);                                              \
   } while (0)
 #define LA_RL(TC)                                                                                                    \
   do {                                                                                                               \
@@ -481,7 +492,7 @@ GB_OP(gb_op_latent_attention) {
   GB_CHECK_LAUNCH("latent_attention");
   if (splits == 1) return 1;
   gb_launch(latent_attention_merge_kernel, dim3(gb_div_up((long long)n * H, 4)), dim3(128), 0, ctx->stream, ws, splits,
-            op_ptr<const float>(a[9]), a[10], op_ptr<float>(a[11]), a[12], n, H, r);
+            op_ptr<const float>(a[9]), a[10], op_ptr<float>(a[11]), a[12], n, H, r, op_ptr<const float>(a[20]));
   GB_CHECK_LAUNCH("latent_attention_merge");
   return 2;
 }

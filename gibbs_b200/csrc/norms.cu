@@ -6,6 +6,10 @@
 //  gb_op_clamped_glu     out = g' * sigmoid(alpha g') * (u' + up_add) for rows [g | u] with clamps
 //  gb_op_gelu_mul_rows   g = gelu_tanh(g) * table[id, offset : offset + dim] (a per-token input)
 //  gb_op_gated_group_norm  out = rmsnorm_in_groups(y * silu(z)) * gain
+//  gb_op_act_rows        out = act(x), act one of gelu (erf), gelu (tanh), silu, relu: the unit of a feed-forward
+//                        without a gate
+//  gb_op_head_norm       per head: out = rmsnorm(x - lambda * x2) * gain * sigmoid(gate) * factor, each of x2,
+//                        gain and gate optional: the norm behind a recurrence or behind two attention maps
 #include "hybrid.cuh"
 
 namespace {
@@ -202,6 +206,62 @@ __global__ void gated_group_norm_kernel(const float* y, long long ldy, const flo
     o[d] = from_f32<TO>(yr[d] * hy_silu(zr[d]) * rstd * gain[c0 + d]);
 }
 
+enum { ACT_GELU_ERF = 0, ACT_GELU_TANH = 1, ACT_SILU = 2, ACT_RELU = 3 };
+
+__device__ __forceinline__ float act_value(float z, int kind) {
+  switch (kind) {
+    case ACT_GELU_ERF: return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f));
+    case ACT_GELU_TANH: return hy_gelu_tanh(z);
+    case ACT_SILU: return hy_silu(z);
+    default: return fmaxf(z, 0.f);
+  }
+}
+
+template <typename TO>
+__global__ void act_rows_kernel(const float* x, long long ld, TO* out, long long ldo, int n, int inner, int kind) {
+  pdl_trigger();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)n * inner) return;
+  const int t = (int)(i / inner), c = (int)(i - (long long)t * inner);
+  out[(size_t)t * ldo + c] = from_f32<TO>(act_value(x[(size_t)t * ld + c], kind));
+}
+
+// one warp per (row, head); values of up to 32 * HN_VR entries stay in registers
+constexpr int HN_VR = 8;
+
+template <typename TO>
+__global__ void head_norm_kernel(const float* x, long long ldx, long long xh, const float* x2,
+                                 const float* __restrict__ gain, const float* gate, long long ld_gate, TO* out,
+                                 long long ldo, int n, int H, int vdim, float eps, float lambda, float factor) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long idx = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (idx >= (long long)n * H) return;
+  const int t = (int)(idx / H), h = (int)(idx - (long long)t * H);
+  const size_t at = (size_t)t * ldx + (size_t)h * xh;
+  float v[HN_VR];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < HN_VR; ++i) {
+    const int d = lane + 32 * i;
+    v[i] = 0.f;
+    if (d < vdim) v[i] = x2 ? x[at + d] - lambda * x2[at + d] : x[at + d];
+    ss += v[i] * v[i];
+  }
+  const float rstd = factor / sqrtf(warp_sum(ss) / (float)vdim + eps);
+#pragma unroll
+  for (int i = 0; i < HN_VR; ++i) {
+    const int d = lane + 32 * i;
+    if (d >= vdim) continue;
+    float o = v[i] * rstd;
+    if (gain) o *= gain[d];
+    if (gate) o *= hy_sigmoid(gate[(size_t)t * ld_gate + (size_t)h * vdim + d]);
+    out[(size_t)t * ldo + (size_t)h * vdim + d] = from_f32<TO>(o);
+  }
+}
+
 inline int norm_threads(int dim) { return dim <= 256 ? 64 : dim <= 1024 ? 128 : 256; }
 
 }  // namespace
@@ -299,5 +359,43 @@ GB_OP(gb_op_gated_group_norm) {
     gb_launch(gated_group_norm_kernel<float>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1],
               op_ptr<const float>(a[2]), a[3], op_ptr<const float>(a[4]), op_ptr<float>(a[5]), a[7], inner, groups, (float)f[0]);
   GB_CHECK_LAUNCH("gated_group_norm");
+  return 1;
+}
+
+// a0 x (f32), a1 its row stride, a2 out [rows, inner], a3 out dtype, a4 its row stride, a5 rows, a6 inner, a7 which
+// function: 0 gelu (erf), 1 gelu (tanh), 2 silu, 3 relu
+GB_OP(gb_op_act_rows) {
+  const int n = (int)a[5], inner = (int)a[6];
+  if (n <= 0) return 0;
+  if (a[7] > ACT_RELU) GB_FAIL(GB_ERR_ARG, "act_rows: function %lld", a[7]);
+  const dim3 grid(gb_div_up((long long)n * inner, 256)), block(256);
+  if (a[3] == GB_BF16)
+    gb_launch(act_rows_kernel<bf16>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], op_ptr<bf16>(a[2]), a[4],
+              n, inner, (int)a[7]);
+  else
+    gb_launch(act_rows_kernel<float>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], op_ptr<float>(a[2]),
+              a[4], n, inner, (int)a[7]);
+  GB_CHECK_LAUNCH("act_rows");
+  return 1;
+}
+
+// a0 x (f32; head h of row t starts at t * a1 + h * a2), a1 row stride, a2 elements between heads, a3 x2 (f32, laid
+// out as x) or 0, a4 gain [vdim] (shared by the heads) or 0, a5 gate logits (f32, [t, h * vdim + d] at a row stride)
+// or 0, a6 that stride, a7 out [rows, heads * vdim], a8 out dtype, a9 its row stride, a10 rows, a11 heads, a12 vdim;
+// f0 eps, f1 lambda, f2 factor
+GB_OP(gb_op_head_norm) {
+  const int n = (int)a[10], H = (int)a[11], vdim = (int)a[12];
+  if (n <= 0) return 0;
+  if (vdim > 32 * HN_VR) GB_FAIL(GB_ERR_ARG, "head_norm: heads of %d values (at most %d)", vdim, 32 * HN_VR);
+  const dim3 grid(gb_div_up((long long)n * H, 4)), block(128);
+  if (a[8] == GB_BF16)
+    gb_launch(head_norm_kernel<bf16>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], a[2],
+              op_ptr<const float>(a[3]), op_ptr<const float>(a[4]), op_ptr<const float>(a[5]), a[6], op_ptr<bf16>(a[7]), a[9],
+              n, H, vdim, (float)f[0], (float)f[1], (float)f[2]);
+  else
+    gb_launch(head_norm_kernel<float>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], a[2],
+              op_ptr<const float>(a[3]), op_ptr<const float>(a[4]), op_ptr<const float>(a[5]), a[6], op_ptr<float>(a[7]), a[9],
+              n, H, vdim, (float)f[0], (float)f[1], (float)f[2]);
+  GB_CHECK_LAUNCH("head_norm");
   return 1;
 }

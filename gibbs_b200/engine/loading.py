@@ -35,7 +35,8 @@ def load_model(folder, dtype="bfloat16", device="cuda:0", arch: Optional[str] = 
         raise FileNotFoundError(f"{folder} has no config.json")
     cfg = json.loads(cfg_path.read_text())
     ckpt = Checkpoint(folder)
-    conf = parse_config(cfg, ckpt.names(), forced=arch)
+    # (a mapping from name to shape: iterating it gives the names; a design may read sizes from shapes)
+    conf = parse_config(cfg, {n: tuple(ckpt.shape(n)) for n in ckpt.names()}, forced=arch)
     model = build_model(conf.plan(), ckpt, parse_dtype(dtype), device)
     model.config = conf
     return model

@@ -1,6 +1,6 @@
 """Bindings of the "hybrid" kernel library (csrc/norms.cu, latent_attention.cu,
-gated_attention.cu, gated_attention_tc.cu, ssm.cu, moe.cu): layer norms, clamped gated units, latent
-attention, gated attention with a sink, state-space recurrences and routed experts.
+gated_attention.cu, gated_attention_tc.cu, ssm.cu, delta_rule.cu, moe.cu): layer norms, clamped gated units, latent
+attention, gated attention with a sink, state-space and delta-rule recurrences and routed experts.
 
 Every operation of that library has the signature of a step-plan operation,
 ``int op(ctx, a[24], f[3], flags)``.  So an operation is described ONCE, by
@@ -22,7 +22,8 @@ LIBRARY = "hybrid"
 OPERATIONS = ("row_norm", "norm_add", "clamped_glu", "gelu_mul_rows", "gated_group_norm", "causal_conv_silu",
               "ssm_scan", "latent_prep", "head_linear", "latent_attention", "moe_route", "moe_sort", "moe_gather",
               "moe_experts", "moe_experts_tc", "moe_combine", "moe_route_grouped", "moe_combine_weighted",
-              "embed_scaled", "qk_prep", "sink_attention", "sink_attention_tc")
+              "embed_scaled", "qk_prep", "sink_attention", "sink_attention_tc", "act_rows", "head_norm", "delta_prep",
+              "delta_scan")
 
 NORM_LAYER, NORM_RMS = 0, 1
 

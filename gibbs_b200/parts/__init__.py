@@ -1,7 +1,7 @@
 from .base import (Residual, Block, FeedForward, Mixer, Norm, PagedKV, PagedRows, Part, PositionEncoding, Rotary, Runtime, SlotState,
                    TensorDecl, MATRIX, VECTOR, INT_TABLE, part_class, register_part)
 from . import (norm, position, attention, short_conv, ffn, block, embedding,  # noqa: F401  (register the built-in kinds)
-               latent_attention, gated_attention, ssm, glu, token_input)
+               latent_attention, gated_attention, ssm, glu, token_input, diff_attention, delta_rule, mlp)
 from .linear import Linear
 from .model import CausalLM, build_model
 

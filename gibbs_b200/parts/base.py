@@ -76,10 +76,22 @@ class PagedKV:
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
+    # positions are seen in blocks of this many, counted from 0: a position needs the keys of its own block
+    # only, so the pages of earlier blocks go back as soon as a request has moved on (not together with ``window``)
+    block: Optional[int] = None
+
+    def __post_init__(self):
+        if self.window is not None and self.block is not None:
+            raise ValueError("pages are kept for a window or for a block of positions, not both")
 
     @property
     def value_dim(self) -> int:
         return self.head_dim if self.v_head_dim is None else self.v_head_dim
+
+    @property
+    def retention(self):
+        """What groups caches into pools: None (every position), a window length, or ("block", size)."""
+        return ("block", self.block) if self.block is not None else self.window
 
 
 @dataclass(frozen=True)
@@ -89,6 +101,10 @@ class PagedRows:
     value per head (a compressed latent from which both derive, say)."""
     width: int
     window: Optional[int] = None
+
+    @property
+    def retention(self):
+        return self.window
 
 
 @dataclass(frozen=True)

@@ -5,8 +5,8 @@ import torch
 
 from .. import ops
 from ..ops import hybrid
-from .runner import Planned, keep
-from .base import Part, TensorDecl, register_part
+from .runner import Eager, Planned, keep
+from .base import Part, SlotState, TensorDecl, register_part
 from .linear import Linear
 
 
@@ -49,6 +49,52 @@ class TokenEmbedding(Part):
             self._scaled(rn, rn.token_ids, plan.residual)
 
 
+class PairEmbedding(TokenEmbedding):
+    """x[t, :] = table[id_t, :] * scale + pairs[(id_(t-1) * mul_prev + id_t * mul_cur) mod buckets, :]; a
+    sequence's first token takes row ``buckets`` (the last) of ``pairs``.  The id before a portion's first
+    token is per-request state: one int32 in the request's slot, which the kernel reads and then replaces
+    by the portion's last id."""
+
+    @classmethod
+    def declare(cls, params):
+        return {"weight": TensorDecl.of(params["vocab"], params["dim"]),
+                "pairs": TensorDecl.of(int(params["buckets"]) + 1, params["dim"])}
+
+    def __init__(self, params, tensors, rt):
+        super().__init__(params, tensors, rt)
+        self.buckets, self.mul_prev, self.mul_cur = (int(params[k]) for k in ("buckets", "mul_prev", "mul_cur"))
+        if self.buckets < 1:
+            raise ValueError(f"a pair table of {self.buckets} buckets")
+        self.pairs = tensors["pairs"].contiguous()
+        if self.pairs.dtype != self.table.dtype:
+            raise ValueError("the token table and the pair table are stored in different dtypes")
+
+    def kernel_libraries(self):
+        return ("core", hybrid.LIBRARY)
+
+    def cache_needs(self):
+        return [SlotState((1,), torch.int32)]
+
+    def _run(self, rn, out: torch.Tensor, caches) -> None:
+        last = caches[0]
+        rn.op("embed_scaled", [keep(rn, self.table), ops.dtype_code(self.table.dtype), rn.token_ids, out.data_ptr(), rn.N,
+                               self.dim, self.vocab, keep(rn, self.pairs), self.buckets, self.mul_prev, self.mul_cur,
+                               rn.tok_req, rn.tok_pos, rn.q_start, rn.q_len, keep(rn, last.state), last.state.stride(0),
+                               rn.slots(last)], [self.scale], label="embed_pairs")
+
+    def forward(self, ids: torch.Tensor, step=None, caches=None) -> torch.Tensor:
+        if step is None or not caches:
+            raise ValueError("an embedding that looks at the token before needs the step and its state")
+        out = self.rt.empty(ids.numel(), self.dim, dtype=torch.float32)
+        self._run(Eager(self.rt, step), out, caches)
+        return out
+
+    def plan_ops(self, plan, caches=None):
+        if not caches:
+            raise ValueError("an embedding that looks at the token before needs its state")
+        self._run(Planned(plan), plan.residual, caches)
+
+
 class LMHead(Part):
     """logits = z W^T in 32-bit; with ``logit_scale`` they are divided by it, with
     ``softcap`` then passed through cap * tanh(x / cap)
@@ -85,4 +131,5 @@ class LMHead(Part):
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("embedding", "pair_embedding", PairEmbedding)
 register_part("head", "lm_head", LMHead)

@@ -1,5 +1,6 @@
 """Attention over a compressed key/value cache ("latent attention"), with an
-output gate per head and an optional sliding window.
+optional output gate per head, an optional sliding window, an optional rotated
+key part and an optional learned sink in the softmax.
 
 For a token with mixer input h (H heads; per head ``dim`` unrotated and
 ``rot_dim`` rotated query/key entries, values of ``vdim``, latent of ``kv_rank``):
@@ -18,6 +19,12 @@ nothing but cache rows (csrc/latent_attention.cu).  Position i sees the
 positions j with 0 <= i - j < window (all earlier ones without a window).  The
 rotation turns the first ``rot_dims`` entries of a rotated part in adjacent
 pairs by pos * base^(-2i / rot_dims).
+
+Options: ``rot_dim`` 0: no rotated part at all (no positions: q has ``dim``
+entries per head and the cache row is the latent alone); ``gate`` False: no
+output gate (then no tensor ``g``); ``sink`` True: a learned score per head
+(tensor ``sink``) whose exponential is added to the softmax's denominator; it
+has no key and no value and is not scaled.
 """
 from __future__ import annotations
 
@@ -39,16 +46,21 @@ class LatentAttention(BranchPart, Mixer):
     @classmethod
     def declare(cls, params):
         d, H = params["hidden"], params["heads"]
-        dn, dr, dv, r = params["dim"], params["rot_dim"], params["vdim"], params["kv_rank"]
-        return {"q": TensorDecl.of(H * (dn + dr), d), "dkv": TensorDecl.of(r + dr, d),
-                "dkv.norm": TensorDecl.of(r, role=VECTOR), "uk": TensorDecl.of(H * dn, r),
-                "uv": TensorDecl.of(H * dv, r), "g": TensorDecl.of(H, d), "o": TensorDecl.of(d, H * dv)}
+        dn, dr, dv, r = params["dim"], params.get("rot_dim", 0), params["vdim"], params["kv_rank"]
+        t = {"q": TensorDecl.of(H * (dn + dr), d), "dkv": TensorDecl.of(r + dr, d),
+             "dkv.norm": TensorDecl.of(r, role=VECTOR), "uk": TensorDecl.of(H * dn, r),
+             "uv": TensorDecl.of(H * dv, r), "o": TensorDecl.of(d, H * dv)}
+        if params.get("gate", True):
+            t["g"] = TensorDecl.of(H, d)
+        if params.get("sink", False):
+            t["sink"] = TensorDecl.of(H, role=VECTOR)
+        return t
 
     def __init__(self, params, tensors, rt):
         super().__init__(params, tensors, rt)
         p = params
         self.hidden, self.heads = int(p["hidden"]), int(p["heads"])
-        self.dn, self.dr, self.dv, self.r = int(p["dim"]), int(p["rot_dim"]), int(p["vdim"]), int(p["kv_rank"])
+        self.dn, self.dr, self.dv, self.r = int(p["dim"]), int(p.get("rot_dim", 0)), int(p["vdim"]), int(p["kv_rank"])
         self.window = int(p["window"]) if p.get("window") else None
         self.scale, self.eps = float(p["scale"]), float(p["eps"])
         self.rot_dims = int(p.get("rot_dims", self.dr))
@@ -56,7 +68,9 @@ class LatentAttention(BranchPart, Mixer):
             raise ValueError(f"{self.rot_dims} rotated dimensions must be even and at most rot_dim {self.dr}")
         H = self.heads
         # one product for [q | latent, rotated key | gate logits]
-        self.fused = torch.cat([tensors["q"], tensors["dkv"], tensors["g"]], 0).contiguous()
+        self.gated = bool(p.get("gate", True))
+        self.fused = torch.cat([tensors["q"], tensors["dkv"]] + ([tensors["g"]] if self.gated else []), 0).contiguous()
+        self.sink = tensors["sink"].to(torch.float32).contiguous() if p.get("sink", False) else None
         self.dkv_col, self.gate_col = H * (self.dn + self.dr), H * (self.dn + self.dr) + self.r + self.dr
         # per head: W_uk,h^T as [kv_rank, dim] (applied to the query), W_uv,h as [vdim, kv_rank]
         self.uk_t = tensors["uk"].reshape(H, self.dn, self.r).transpose(1, 2).contiguous()
@@ -64,7 +78,7 @@ class LatentAttention(BranchPart, Mixer):
         self.latent_gain = tensors["dkv.norm"].to(torch.float32).contiguous()
         self.o = tensors["o"].contiguous()
         i = np.arange(self.rot_dims // 2, dtype=np.float64)
-        inv = np.power(float(p["rot_base"]), -2.0 * i / max(self.rot_dims, 1))
+        inv = np.power(float(p.get("rot_base", 1.0)), -2.0 * i / max(self.rot_dims, 1))
         self.inv_freq = torch.from_numpy(np.concatenate([inv, [0.0]]).astype(np.float32)).to(rt.device)
 
     def kernel_libraries(self):
@@ -79,7 +93,9 @@ class LatentAttention(BranchPart, Mixer):
             pairs -= (n_tokens - self.window) * (n_tokens - self.window + 1) // 2
         return 2 * self.heads * (2 * self.r + self.dr) * pairs
 
-    def run(self, rn: Runner, h, out, caches):
+    adds_in_place = True       # with ``accumulate`` the output projection adds into the stream
+
+    def run(self, rn: Runner, h, out, caches, accumulate: bool = False):
         view = caches[0]
         if not view.writable:
             raise RuntimeError("latent attention writes the cache it reads")
@@ -101,13 +117,14 @@ class LatentAttention(BranchPart, Mixer):
         ws = rn.buffer("la_partial", r + 2, torch.float32, fixed_rows=_workspace_rows())
         rn.op("latent_attention", [qp.data_ptr(), pages.data_ptr(), ops.dtype_code(pages.dtype), table, bt_stride,
                                    pages.shape[1], pages.shape[0], rn.tok_req, rn.tok_pos,
-                                   fused.data_ptr() + 4 * self.gate_col, fused.stride(0), lat.data_ptr(), lat.stride(0),
-                                   rn.N, H, r, dr, self.window or 0, rn.max_context, ws.data_ptr()], [self.scale])
+                                   fused.data_ptr() + 4 * self.gate_col if self.gated else 0, fused.stride(0),
+                                   lat.data_ptr(), lat.stride(0), rn.N, H, r, dr, self.window or 0, rn.max_context,
+                                   ws.data_ptr(), keep(rn, self.sink)], [self.scale])
         o = rn.buffer("la_heads_out", H * dv)
         rn.op("head_linear", [lat.data_ptr(), lat.stride(0), r, keep(rn, self.uv), ops.dtype_code(self.uv.dtype),
                               o.data_ptr(), ops.dtype_code(o.dtype), o.stride(0), dv, rn.N, H, dv, r],
               label="head_linear:values")
-        rn.linear(o, self.o, None, out, role="latent_out")
+        (rn.add_linear if accumulate else rn.linear)(o, self.o, None, out, role="latent_out")
 
 
 register_part("mixer", "latent_attention", LatentAttention)

@@ -1,0 +1,54 @@
+"""A feed-forward without a gate: out = W_down act(W_up h).
+
+``act`` is one of "gelu" (the exact one, with erf), "gelu_tanh", "silu",
+"relu".  The first product writes 32-bit values, the function is taken in
+32-bit and rounded to the compute dtype for the second product, which adds
+into the residual stream.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..ops import hybrid
+from .base import FeedForward, TensorDecl, VECTOR, register_part
+from .runner import BranchPart, Runner
+
+ACTIVATIONS = {"gelu": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+
+
+class DenseMLP(BranchPart, FeedForward):
+    adds_in_place = True
+
+    @classmethod
+    def declare(cls, params):
+        h, f = params["hidden"], params["inner"]
+        d = {"up": TensorDecl.of(f, h), "down": TensorDecl.of(h, f)}
+        if params.get("bias"):
+            d.update({"up.b": TensorDecl.of(f, role=VECTOR), "down.b": TensorDecl.of(h, role=VECTOR)})
+        return d
+
+    def __init__(self, params, tensors, rt):
+        super().__init__(params, tensors, rt)
+        self.hidden, self.inner = int(params["hidden"]), int(params["inner"])
+        act = params.get("act", "gelu")
+        if act not in ACTIVATIONS:
+            raise ValueError(f"unknown activation '{act}'; known: {sorted(ACTIVATIONS)}")
+        self.act = ACTIVATIONS[act]
+        self.up, self.down = tensors["up"].contiguous(), tensors["down"].contiguous()
+        f32 = lambda n: tensors[n].to(torch.float32).contiguous() if params.get("bias") else None
+        self.up_bias, self.down_bias = f32("up.b"), f32("down.b")
+
+    def kernel_libraries(self):
+        return tuple(set(ops.linear_libraries(self.up.dtype, self.rt.dtype)) | {"core", hybrid.LIBRARY})
+
+    def run(self, rn: Runner, h, out, caches=None, accumulate: bool = False):
+        z = rn.buffer("mlp_up", self.inner, torch.float32)
+        rn.linear(h, self.up, self.up_bias, z, role="mlp_up")
+        act = rn.buffer("mlp_act", self.inner)
+        rn.op("act_rows", [z.data_ptr(), z.stride(0), act.data_ptr(), ops.dtype_code(act.dtype), act.stride(0), rn.N,
+                           self.inner, self.act])
+        (rn.add_linear if accumulate else rn.linear)(act, self.down, self.down_bias, out, role="mlp_down")
+
+
+register_part("feed_forward", "dense_mlp", DenseMLP)

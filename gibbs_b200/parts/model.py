@@ -30,7 +30,12 @@ class CausalLM:
     def entry_needs(self):
         """For each entry of the plan's order: (cache needs of its mixer, the
         entry whose cache it reads instead, or None)."""
-        return [(self.blocks[e.layer].cache_needs(), e.reads_cache_of) for e in self.plan.order]
+        needs = [(self.blocks[e.layer].cache_needs(), e.reads_cache_of) for e in self.plan.order]
+        # an embedding that keeps state per request (the token before) comes behind the order's entries
+        own = getattr(self.embedding, "cache_needs", None)
+        if own is not None and own():
+            needs.append((list(own()), None))
+        return needs
 
     def kernel_libraries(self) -> set[str]:
         libs = {"core"}
@@ -42,7 +47,10 @@ class CausalLM:
     def forward(self, step, caches) -> Optional[torch.Tensor]:
         """Run the step's tokens through every entry of the order; return the
         32-bit logits of the wanted rows, [n_want, vocab], or None."""
-        x = Residual(self.embedding.forward(step.token_ids))
+        if getattr(self.embedding, "cache_needs", None) is not None:
+            x = Residual(self.embedding.forward(step.token_ids, step, caches[len(self.plan.order)]))
+        else:
+            x = Residual(self.embedding.forward(step.token_ids))
         for e, entry in enumerate(self.plan.order):
             self.blocks[entry.layer].forward(x, step, caches[e])
         if step.n_want == 0:
@@ -56,7 +64,10 @@ class CausalLM:
     def plan_ops(self, plan, caches) -> None:
         """Append everything ``forward`` does to a step plan; raises
         NotPlannable if a part cannot be written as operations."""
-        plan_ops_of(self.embedding)(plan)
+        if getattr(self.embedding, "cache_needs", None) is not None:
+            plan_ops_of(self.embedding)(plan, caches[len(self.plan.order)])
+        else:
+            plan_ops_of(self.embedding)(plan)
         for e, entry in enumerate(self.plan.order):
             plan_ops_of(self.blocks[entry.layer])(plan, caches[e])
         if getattr(self.head, "fuses_norm", False) and getattr(self.final_norm, "lazy", None) is not None:

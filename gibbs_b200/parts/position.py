@@ -17,6 +17,22 @@ def _inv_freq_f32(rotary_dim: int, theta: float) -> np.ndarray:
     return (np.float32(1.0) / np.power(np.float32(theta), expo, dtype=np.float32)).astype(np.float32)
 
 
+def stretched_inv_freq(rotary_dim: int, base: float, scaling=None) -> np.ndarray:
+    """f_i = base^(-2i / rotary_dim) in 64-bit, rounded once to 32-bit.  ``scaling`` = {factor, low, high,
+    original} stretches long wavelengths (the rule Llama 3.1 introduced): with l = 2 pi / f, f stays where
+    l < original / high, becomes f / factor where l > original / low, and in between is
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low)."""
+    i = np.arange(rotary_dim // 2, dtype=np.float64)
+    f = np.power(float(base), -2.0 * i / max(rotary_dim, 1))
+    if scaling:
+        factor, low, high, orig = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
+        wl = 2.0 * np.pi / f
+        s = (orig / wl - low) / (high - low) if high != low else np.ones_like(f)
+        mid = (1.0 - s) * f / factor + s * f
+        f = np.where(wl < orig / high, f, np.where(wl > orig / low, f / factor, mid))
+    return f.astype(np.float32)
+
+
 class RotaryHalfSplit(PositionEncoding):
     """Rotates the pairs (j, j + rotary_dim/2) by pos * inv_freq[j]
     (MisterTK/gibbs src/graph/cpu.rs:688-697)."""

@@ -34,6 +34,11 @@ class Runner:
         the product in the timing table."""
         raise NotImplementedError
 
+    def add_linear(self, x, weight, bias, out, role: str = "") -> None:
+        """out += x weight^T (+ bias), for ``out`` the 32-bit residual stream: a sublayer's last product does
+        the residual sum."""
+        raise NotImplementedError
+
     def glu_linear(self, x, weight, out, glu, role: str = "") -> None:
         """out = unit(x weight^T) on the tensor cores, for a weight whose gate and up rows alternate in
         blocks of 64 (``parts.linear.interleave_gate_up``); ``glu`` = (alpha, limit, add)."""
@@ -66,6 +71,9 @@ class Eager(Runner):
     def linear(self, x, weight, bias, out, role=""):
         ops.linear(x[:self.N] if x.shape[0] != self.N else x, weight, bias, out)
 
+    def add_linear(self, x, weight, bias, out, role=""):
+        ops.linear(x[:self.N] if x.shape[0] != self.N else x, weight, bias, out, True)
+
     def glu_linear(self, x, weight, out, glu, role=""):
         ops.linear_tc(x[:self.N] if x.shape[0] != self.N else x, weight, None, out, swiglu=True, glu=glu)
 
@@ -97,6 +105,11 @@ class Planned(Runner):
 
     def linear(self, x, weight, bias, out, role=""):
         self.plan.linear(x, weight, bias, out, "plain", role=role or "plain")
+
+    def add_linear(self, x, weight, bias, out, role=""):
+        if out is not self.plan.residual:
+            raise NotPlannable("a plan's products add into the plan's own residual stream")
+        self.plan.linear(x, weight, bias, None, "residual", role=role or "residual")
 
     def glu_linear(self, x, weight, out, glu, role=""):
         self.plan.linear(x, weight, None, out, "swiglu", role=role or "glu", glu=glu)
