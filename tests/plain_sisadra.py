@@ -25,11 +25,13 @@ def rms(x, eps):
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
 
 
-def embed(tokens, table, bigram, scale, buckets, mul_prev, mul_cur):
-    """Row of the token times ``scale`` plus a row of the pair table chosen by a hash of
+def embed(tokens, table, scale, bigram=None, buckets=0, mul_prev=0, mul_cur=0):
+    """Row of the token times ``scale``; with a pair table plus a row of it chosen by a hash of
     (token before, token); the first token of a sequence takes the table's last row."""
     ids = torch.as_tensor(tokens, dtype=torch.long)
     x = table[ids] * scale
+    if bigram is None:
+        return x
     rows = torch.empty_like(ids)
     rows[0] = buckets
     rows[1:] = (ids[:-1] * mul_prev + ids[1:] * mul_cur) % buckets
@@ -195,9 +197,12 @@ def forward(cfg, tensors, tokens, want=None, layers_out=None):
     stream after every layer."""
     eps = float(cfg["norm"]["eps"])
     e = cfg.get("embedding") or {}
-    b = e["bigram"]
-    x = embed(tokens, tensors["embed"].to(F64), tensors["bigram"].to(F64), float(e.get("scale", 1.0)),
-              int(b["buckets"]), int(b["mul_prev"]), int(b["mul_cur"]))
+    b = e.get("bigram")
+    if b is None:
+        x = embed(tokens, tensors["embed"].to(F64), float(e.get("scale", 1.0)))
+    else:
+        x = embed(tokens, tensors["embed"].to(F64), float(e.get("scale", 1.0)), tensors["bigram"].to(F64),
+                  int(b["buckets"]), int(b["mul_prev"]), int(b["mul_cur"]))
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
         h = layer_norm(x, tensors[p + "norm1"].to(F64), eps)

@@ -179,3 +179,35 @@ def test_trace_run_petelix_with_and_without_dependent_launch(tmp_path):
     for rid in results["serial"]:
         for p in results["serial"][rid]:
             assert np.array_equal(results["serial"][rid][p], results["overlapped"][rid][p]), (rid, p)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_sisadra_from_a_folder_without_rank_keys(tmp_path, dtype):
+    """The Sisadra design through the same runner: a model folder on disk whose config.json does not name the
+    ranks of the low-rank projections (the checkpoint's shapes give them), mixed steps with sparse wants in a
+    pool that makes pages and the four state slots go round (two groups of pages kept by blocks, one that
+    keeps everything)."""
+    import copy
+    import plain_sisadra
+    from potivik_helpers import rel_rows, write_model
+    from sisadra_helpers import CFG_A, make_weights
+    W = make_weights(CFG_A, 31)
+    cfg = copy.deepcopy(CFG_A)
+    for layer in cfg["layers"]:
+        layer["mixer"].pop("decay_rank", None), layer["mixer"].pop("gate_rank", None)
+    folder = write_model(tmp_path / "sisadra_a", cfg, W)
+    vocab = cfg["vocab"]
+    reqs = {f"q{i}": random_ids(60 + i, n, vocab) for i, n in enumerate([70, 45, 130, 1, 64, 20, 33])}
+    steps = trace_mixed(reqs, capacity_tokens=320, max_live=4, seed=6)
+    for k, s in enumerate(steps):
+        for e in s["entries"]:
+            e["want"] = [] if k % 5 == 4 else [w for w in e["want"] if (w + k) % 3]
+    want = {rid: plain_sisadra.forward(CFG_A, W, ids).numpy() for rid, ids in reqs.items()}
+    out = tmp_path / "out"
+    _run(folder, dtype, steps, out, max_tokens=320)
+    got = _collect(steps, out, vocab)
+    for rid in reqs:
+        rows = sorted(got.get(rid, {}))
+        if rows:
+            e = rel_rows(np.stack([got[rid][p] for p in rows]), want[rid][rows])
+            assert e.max() <= (2e-4 if dtype == "float32" else 4e-2), f"{rid}: place {rows[int(e.argmax())]} differs by {e.max():.3g}"
