@@ -90,12 +90,37 @@ def petelix_shape(size: str) -> dict:
             "layers": layers}
 
 
+def sisadra_shape(size: str) -> dict:
+    """Layer sizes that resemble a real model's, for the Sisadra design: delta-rule layers in turn with
+    differential attention in blocks and latent attention, a dense feed-forward behind each."""
+    if size == "1k":
+        d, vocab = 1024, 32768
+        rule = {"heads": 16, "kv_heads": 8, "dim": 64, "vdim": 64, "conv": 4, "decay_rank": 64, "gate_rank": 64}
+        att = {"heads": 8, "kv_heads": 2, "dim": 64, "vdim": 128, "scale": 0.125, "diff": 0.3, "mask": {"size": 512},
+               "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+        lat = {"heads": 8, "dim": 64, "vdim": 64, "kv_rank": 256, "scale": 0.125}
+    else:
+        d, vocab = 2048, 65536
+        rule = {"heads": 16, "kv_heads": 8, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 128, "gate_rank": 128}
+        att = {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 128, "scale": 0.125, "diff": 0.3, "mask": {"size": 1024},
+               "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+        lat = {"heads": 16, "dim": 128, "vdim": 128, "kv_rank": 512, "scale": 128 ** -0.5}
+    mlp = {"kind": "dense", "ff": 4 * d}
+    kinds = ["channel_delta", "attention", "channel_delta", "latent_attention"] * 2
+    mixers = {"channel_delta": rule, "attention": att, "latent_attention": lat}
+    return {"architecture": "Sisadra", "vocab": vocab, "width": d, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+            "embedding": {"scale": 8.0, "bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 999983}},
+            "layers": [{"type": k, "mixer": mixers[k], "mlp": mlp} for k in kinds]}
+
+
 def potivik_workload(a):
     """Prompt and decode throughput of the Potivik design at two sizes (random weights), beside an LFM2
     model of equal width, depth and feed-forward width, with the time per kind of operation of one
     prompt step and one decode step (the walker's timing mode).  One JSON line per model and size.
     'petelix': the same for the Petelix design, beside an LFM2 model whose layers are all attention layers
-    and whose feed-forward is as wide as the experts a token uses."""
+    and whose feed-forward is as wide as the experts a token uses.  'sisadra': the same for the Sisadra design,
+    beside an LFM2 model and a Potivik model (state-space and latent-attention layers in turn) of equal width,
+    depth and feed-forward width."""
     import torch
     from gibbs_b200 import Engine, Lfm2Config, parse_config, random_model
     from gibbs_b200.engine import benchmark as B
@@ -108,13 +133,22 @@ def potivik_workload(a):
                         num_key_value_heads=m["kv_heads"], head_dim=m["dim"], vocab_size=pot["vocab"],
                         intermediate_size=r["top"] * pot["layers"][0]["mlp"]["expert"]["ff"], block_auto_adjust_ff_dim=False,
                         full_attn_idxs=list(range(8)), max_position_embeddings=4096)
+        elif a.workload == "sisadra":
+            pot = sisadra_shape(size)
+            d = pot["width"]
+            twin = dict(LFM2_1P2B, hidden_size=d, num_hidden_layers=8, num_attention_heads=d // 64, num_key_value_heads=d // 256,
+                        head_dim=64, vocab_size=pot["vocab"], intermediate_size=4 * d, block_auto_adjust_ff_dim=False,
+                        full_attn_idxs=[1, 3, 5, 7], max_position_embeddings=4096)
         else:
             pot = potivik_shape(size)
             d = pot["width"]
             twin = dict(LFM2_1P2B, hidden_size=d, num_hidden_layers=8, num_attention_heads=d // 64, num_key_value_heads=d // 256,
                         head_dim=64, vocab_size=pot["vocab"], intermediate_size=4 * d, block_auto_adjust_ff_dim=False,
                         full_attn_idxs=[1, 3, 5, 7], max_position_embeddings=4096)
-        for name, conf in ((pot["architecture"], parse_config(pot)), ("LFM2 of equal size", Lfm2Config.from_dict(twin))):
+        models = [(pot["architecture"], parse_config(pot)), ("LFM2 of equal size", Lfm2Config.from_dict(twin))]
+        if a.workload == "sisadra":
+            models.append(("Potivik of equal size", parse_config(potivik_shape(size))))
+        for name, conf in models:
             model = random_model(conf, SEED, dtype="bfloat16", device="cuda:0", stored_dtype=torch.bfloat16)
             eng = Engine(model, n_pages=(batch + 1) * (4096 // 16), page_size=16, max_requests=batch, max_step_tokens=prompt,
                          max_context=4096)
@@ -205,10 +239,10 @@ def main():
                     help="float32: the engine's true 32-bit twin on the same (bfloat16-rounded) weights; "
                          "with --only prefill or --only decode (the benchmark line itself is bfloat16)")
     ap.add_argument("--skip-points", action="store_true", help="skip batch 1 and 64")
-    ap.add_argument("--workload", choices=["serve700m", "long2p6b", "sweep", "potivik", "petelix"], default=None,
-                    help="run one of the other workloads instead (prints its own JSON lines); 'potivik' / 'petelix': that "
-                         "design at layer sizes of a real model, beside an LFM2 model of equal size")
-    ap.add_argument("--size", default=None, help="with --workload potivik or petelix: '1k', '2k' or both with a comma (default both)")
+    ap.add_argument("--workload", choices=["serve700m", "long2p6b", "sweep", "potivik", "petelix", "sisadra"], default=None,
+                    help="run one of the other workloads instead (prints its own JSON lines); 'potivik' / 'petelix' / "
+                         "'sisadra': that design at layer sizes of a real model, beside an LFM2 model of equal size")
+    ap.add_argument("--size", default=None, help="with --workload potivik, petelix or sisadra: '1k', '2k' or both with a comma (default both)")
     ap.add_argument("--prompt-tokens", type=int, default=None,
                     help="with --only prefill / prefill-timeline / products: another prompt length than 2,048")
     ap.add_argument("--only", default=None,
@@ -231,7 +265,7 @@ def main():
     from gibbs_b200 import Generator, Lfm2Config, random_model
     from gibbs_b200.engine import benchmark as B
 
-    if a.workload in ("potivik", "petelix"):
+    if a.workload in ("potivik", "petelix", "sisadra"):
         return potivik_workload(a)
     if a.workload:
         return other_workload(a)

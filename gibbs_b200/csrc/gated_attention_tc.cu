@@ -8,6 +8,12 @@
 // exponentials, maxima and sums in 32-bit.  The weights enter the second product as TWO bfloat16 terms
 // (p = hi + lo, O += hi V + lo V), which keeps 16 bits of every weight.  With several chunks of keys
 // (blockIdx.z) a CTA leaves (maximum, sum, weighted sum) per row for the merge kernel of gated_attention.cu.
+//
+// With `maps` > 1 a query head is `maps` heads of DK entries side by side and a key row of the pages holds
+// `maps` keys side by side; every map is an attention of its own over the same values with an output of its
+// own (differential attention combines them afterwards).  A CTA then takes one (kv head, map) pair.  With
+// `blocked` a position sees the positions of its own block of `window` positions, counted from 0, instead
+// of the last `window`.  The output is bfloat16 or, for what is combined in 32-bit afterwards, 32-bit.
 #include <cuda_bf16.h>
 
 #include "hybrid.cuh"
@@ -68,8 +74,8 @@ struct TcParams {
   const int* block_table; int bt_stride, page_size, n_pages;
   const int* tok_req; const int* tok_pos; const int* q_start;
   const float* gate; long long ld_gate;
-  bf16* out; long long ldo;
-  int N, R, H, G, tokens_per_tile;
+  bf16* out; float* out_f32; long long ldo;      // one of the two
+  int N, R, H, G, tokens_per_tile, maps, blocked;
   float scale, softcap;
   int window, sink, splits, chunk;
   float* ws; int* status;
@@ -87,7 +93,8 @@ __global__ void __launch_bounds__(TC_THREADS, (DK + DV <= 128) ? 4 : 2) sink_att
   bf16* Vs = Ks + 2 * TC_KT * KS;                            // [2][TC_KT][VS]
   pdl_trigger();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int group = p.H / p.G, g = blockIdx.y, tpt = p.tokens_per_tile;
+  const int group = p.H / p.G, tpt = p.tokens_per_tile;
+  const int g = blockIdx.y / p.maps, mp = blockIdx.y - g * p.maps;      // kv head and map
   // this CTA's request and first token: the tiles of the step's requests, one request after the other
   int tile = blockIdx.x, t0 = -1, n_tok = 0;
   for (int r = 0; r < p.R; ++r) {
@@ -104,7 +111,7 @@ __global__ void __launch_bounds__(TC_THREADS, (DK + DV <= 128) ? 4 : 2) sink_att
   const int pos0 = p.tok_pos[t0];
   const int* table = p.block_table + (size_t)p.tok_req[t0] * p.bt_stride;
   const int n_rows = n_tok * group;
-  const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int lo = p.window > 0 ? (p.blocked ? (pos0 / p.window) * p.window : max(0, pos0 - p.window + 1)) : 0;
   const int k_begin = p.splits > 1 ? lo + (int)blockIdx.z * p.chunk : lo;
   const int k_end = p.splits > 1 ? min(pos0 + n_tok - 1, k_begin + p.chunk - 1) : pos0 + n_tok - 1;
   const int n_tiles = k_end >= k_begin ? (k_end - k_begin) / TC_KT + 1 : 0;
@@ -123,7 +130,7 @@ __global__ void __launch_bounds__(TC_THREADS, (DK + DV <= 128) ? 4 : 2) sink_att
       if (page < 0 || page >= p.n_pages) atomicExch(p.status, STATUS_BAD_PAGE_READ);
       else row = ((long long)page * p.G + g) * p.page_size + kp % p.page_size;
     }
-    const bf16* ksrc = p.k_pages + (row < 0 ? 0 : row) * DK;
+    const bf16* ksrc = p.k_pages + ((row < 0 ? 0 : row) * p.maps + mp) * DK;
     const bf16* vsrc = p.v_pages + (row < 0 ? 0 : row) * DV;
 #pragma unroll
     for (int i = 0; i < HALF; ++i) {
@@ -140,7 +147,8 @@ __global__ void __launch_bounds__(TC_THREADS, (DK + DV <= 128) ? 4 : 2) sink_att
     const int R = c / (DK / 8), part = c - R * (DK / 8);
     const bool valid = R < n_rows;
     const int tt = valid ? R / group : 0, hh = valid ? R - tt * group : 0;
-    cp16_zfill(Qs + R * KS + part * 8, p.q + (size_t)(t0 + tt) * p.ldq + (size_t)(g * group + hh) * DK + part * 8, valid);
+    cp16_zfill(Qs + R * KS + part * 8,
+               p.q + (size_t)(t0 + tt) * p.ldq + ((size_t)(g * group + hh) * p.maps + mp) * DK + part * 8, valid);
   }
   cp_commit();
   if (n_tiles > 0) load_kv(0, 0);
@@ -161,7 +169,8 @@ __global__ void __launch_bounds__(TC_THREADS, (DK + DV <= 128) ? 4 : 2) sink_att
   // this thread's two rows and their positions
   const int r_lo = rb + (lane >> 2), r_hi = r_lo + 8;
   const int pos_lo = r_lo < n_rows ? pos0 + r_lo / group : -1, pos_hi = r_hi < n_rows ? pos0 + r_hi / group : -1;
-  const int first_lo = p.window > 0 ? pos_lo - p.window + 1 : 0, first_hi = p.window > 0 ? pos_hi - p.window + 1 : 0;
+  const int first_lo = p.window <= 0 ? 0 : p.blocked ? (max(pos_lo, 0) / p.window) * p.window : pos_lo - p.window + 1;
+  const int first_hi = p.window <= 0 ? 0 : p.blocked ? (max(pos_hi, 0) / p.window) * p.window : pos_hi - p.window + 1;
   float o[DV / 8][4];
 #pragma unroll
   for (int n = 0; n < DV / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
@@ -185,8 +194,8 @@ __global__ void __launch_bounds__(TC_THREADS, (DK + DV <= 128) ? 4 : 2) sink_att
       const bf16* vb = Vs + (it & 1) * TC_KT * VS;
       const int k0 = k_begin + it * TC_KT;
       // every row of the tile sees every key of this key tile: nothing to mask
-      const bool all_seen = k0 + TC_KT - 1 <= min(pos0, k_end) && (p.window <= 0 || k0 > pos_last - p.window) &&
-                            n_rows - rb >= 16;
+      const bool all_seen = k0 + TC_KT - 1 <= min(pos0, k_end) && n_rows - rb >= 16 &&
+                            (p.window <= 0 || (p.blocked ? k0 >= (pos_last / p.window) * p.window : k0 > pos_last - p.window));
       float s[2 * NB][4];
 #pragma unroll
       for (int n = 0; n < 2 * NB; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
@@ -286,7 +295,7 @@ __global__ void __launch_bounds__(TC_THREADS, (DK + DV <= 128) ? 4 : 2) sink_att
     __syncthreads();
     for (int idx = tid; idx < n_rows * DV; idx += TC_THREADS) {
       const int R = idx / DV, d = idx - R * DV;
-      const int tt = R / group, h = g * group + (R - tt * group), t = t0 + tt;
+      const int tt = R / group, h = (g * group + (R - tt * group)) * p.maps + mp, t = t0 + tt;
       float m = -INFINITY;
 #pragma unroll
       for (int w = 0; w < 4; ++w) m = fmaxf(m, part[((size_t)w * 16 + R) * (DV + 2)]);
@@ -301,7 +310,7 @@ __global__ void __launch_bounds__(TC_THREADS, (DK + DV <= 128) ? 4 : 2) sink_att
         }
       }
       if (p.splits > 1) {
-        float* w = p.ws + (((size_t)t * p.H + h) * p.splits + blockIdx.z) * (DV + 2);
+        float* w = p.ws + (((size_t)t * p.H * p.maps + h) * p.splits + blockIdx.z) * (DV + 2);
         if (d == 0) { w[0] = m; w[1] = l; }
         w[2 + d] = acc;
         continue;
@@ -310,7 +319,9 @@ __global__ void __launch_bounds__(TC_THREADS, (DK + DV <= 128) ? 4 : 2) sink_att
       const float e = expf(m - M);
       const float inv = 1.0f / fmaf(e, l, p.sink ? expf(0.f - M) : 0.f);
       const float gt = p.gate ? hy_sigmoid(p.gate[(size_t)t * p.ld_gate + (size_t)h * DV + d]) : 1.f;
-      p.out[(size_t)t * p.ldo + (size_t)h * DV + d] = __float2bfloat16_rn(fmaf(e, acc, 0.f) * inv * gt);
+      const float val = fmaf(e, acc, 0.f) * inv * gt;
+      if (p.out_f32) p.out_f32[(size_t)t * p.ldo + (size_t)h * DV + d] = val;
+      else p.out[(size_t)t * p.ldo + (size_t)h * DV + d] = __float2bfloat16_rn(val);
     }
     return;
   }
@@ -319,10 +330,10 @@ __global__ void __launch_bounds__(TC_THREADS, (DK + DV <= 128) ? 4 : 2) sink_att
   for (int half = 0; half < 2; ++half) {
     const int R = half ? r_hi : r_lo;
     if (R >= n_rows) continue;
-    const int tt = R / group, h = g * group + (R - tt * group), t = t0 + tt;
+    const int tt = R / group, h = (g * group + (R - tt * group)) * p.maps + mp, t = t0 + tt;
     const float m = half ? m_hi : m_lo, l = half ? l_hi : l_lo;
     if (p.splits > 1) {
-      float* w = p.ws + (((size_t)t * p.H + h) * p.splits + blockIdx.z) * (DV + 2);
+      float* w = p.ws + (((size_t)t * p.H * p.maps + h) * p.splits + blockIdx.z) * (DV + 2);
       if ((lane & 3) == 0) { w[0] = m; w[1] = l; }
 #pragma unroll
       for (int n = 0; n < DV / 8; ++n) {
@@ -336,13 +347,14 @@ __global__ void __launch_bounds__(TC_THREADS, (DK + DV <= 128) ? 4 : 2) sink_att
     const float e = expf(m - M);
     const float inv = 1.0f / fmaf(e, l, p.sink ? expf(0.f - M) : 0.f);
     const float* gt = p.gate ? p.gate + (size_t)t * p.ld_gate + (size_t)h * DV : nullptr;
-    bf16* dst = p.out + (size_t)t * p.ldo + (size_t)h * DV;
+    const size_t at = (size_t)t * p.ldo + (size_t)h * DV;
 #pragma unroll
     for (int n = 0; n < DV / 8; ++n) {
       const int d = n * 8 + (lane & 3) * 2;
       const float g0 = gt ? hy_sigmoid(gt[d]) : 1.f, g1 = gt ? hy_sigmoid(gt[d + 1]) : 1.f;
-      *reinterpret_cast<__nv_bfloat162*>(dst + d) =
-          __floats2bfloat162_rn(fmaf(e, o[n][2 * half], 0.f) * inv * g0, fmaf(e, o[n][2 * half + 1], 0.f) * inv * g1);
+      const float v0 = fmaf(e, o[n][2 * half], 0.f) * inv * g0, v1 = fmaf(e, o[n][2 * half + 1], 0.f) * inv * g1;
+      if (p.out_f32) *reinterpret_cast<float2*>(p.out_f32 + at + d) = make_float2(v0, v1);
+      else *reinterpret_cast<__nv_bfloat162*>(p.out + at + d) = __floats2bfloat162_rn(v0, v1);
     }
   }
 }
@@ -381,22 +393,30 @@ GB_API int gb_sink_attention_tc_supported(int heads, int kv_heads, int dim, int 
 // stride, a11 out [tokens, heads * vdim] (bf16), a12 its row stride, a13 tokens, a14 heads, a15 kv heads, a16 dim,
 // a17 vdim, a18 window (0: every earlier position), a19 longest context of the step (an upper bound will do), a20
 // workspace for partial results (gb_sink_attention_workspace_rows() rows of vdim + 2 floats) or 0, a21 requests, a22
-// row of each request's first token [requests]; flags bit 0: the softmax has a sink; f0 scale, f1 soft cap (0: none)
+// row of each request's first token [requests]; flags bit 0: the softmax has a sink, bit 1: out is 32-bit (else
+// bfloat16), bit 2: a position sees its own block of `window` positions, counted from 0, bits 8 to 11: maps (0 means
+// 1): q is [tokens, heads * maps * dim], a key row [maps * dim], out [tokens, heads * maps * vdim]; f0 scale, f1 soft
+// cap (0: none)
 GB_OP(gb_op_sink_attention_tc) {
   const int n = (int)a[13], H = (int)a[14], G = (int)a[15], dim = (int)a[16], vdim = (int)a[17], R = (int)a[21];
   if (n <= 0 || R <= 0) return 0;
   if (!gb_sink_attention_tc_supported(H, G, dim, vdim))
     GB_FAIL(GB_ERR_ARG, "sink_attention_tc: %d heads over %d kv heads of %d / %d entries are not built", H, G, dim, vdim);
-  if ((a[0] & 15) || (a[1] & 15) || (a[2] & 15) || (a[11] & 3) || (a[12] & 1))
+  const int maps = ((flags >> 8) & 15) ? ((flags >> 8) & 15) : 1;
+  const bool out_f32 = flags & 2;
+  if ((a[0] & 15) || (a[1] & 15) || (a[2] & 15) || (a[11] & (out_f32 ? 7 : 3)) || (a[12] & 1))
     GB_FAIL(GB_ERR_ARG, "sink_attention_tc: operands are not aligned for 16-byte copies");
+  if ((flags & 4) && a[18] <= 0) GB_FAIL(GB_ERR_ARG, "sink_attention_tc: blocks of %lld positions", a[18]);
+  if (maps > 1 && a[9]) GB_FAIL(GB_ERR_ARG, "sink_attention_tc: no output gate with several maps");
   const int group = H / G;
   TcParams p;
-  p.q = op_ptr<const bf16>(a[0]); p.ldq = (long long)H * dim;
+  p.maps = maps; p.blocked = (flags & 4) ? 1 : 0;
+  p.q = op_ptr<const bf16>(a[0]); p.ldq = (long long)H * maps * dim;
   p.k_pages = op_ptr<const bf16>(a[1]); p.v_pages = op_ptr<const bf16>(a[2]);
   p.block_table = op_ptr<const int>(a[3]); p.bt_stride = (int)a[4]; p.page_size = (int)a[5]; p.n_pages = (int)a[6];
   p.tok_req = op_ptr<const int>(a[7]); p.tok_pos = op_ptr<const int>(a[8]); p.q_start = op_ptr<const int>(a[22]);
   p.gate = op_ptr<const float>(a[9]); p.ld_gate = a[10];
-  p.out = op_ptr<bf16>(a[11]); p.ldo = a[12];
+  p.out = out_f32 ? nullptr : op_ptr<bf16>(a[11]); p.out_f32 = out_f32 ? op_ptr<float>(a[11]) : nullptr; p.ldo = a[12];
   // every request brings one token (n == R) and its heads fill at most 16 rows: tiles of one token, whose key tiles
   // the four warps split
   const bool narrow = n == R && group <= 16;
@@ -409,7 +429,7 @@ GB_OP(gb_op_sink_attention_tc) {
   // chunks of keys when the tiles alone leave the GPU idle (decoding); whole key tiles, at fixed distances from the
   // first visible key; with a window the cut depends on the launch's sizes only
   const int span = p.window > 0 ? p.window + p.tokens_per_tile : (a[19] > 0 ? (int)a[19] : 1);
-  int wanted = 592 / (tiles * G);
+  int wanted = 592 / (tiles * G * maps);
   if (wanted > 32) wanted = 32;
   p.splits = 1; p.chunk = span;
   if (wanted > 1 && p.ws != nullptr && !(p.window > 0 && span <= TC_KT)) {
@@ -421,12 +441,12 @@ GB_OP(gb_op_sink_attention_tc) {
       while (gb_div_up(span, chunk) > 2 * wanted) chunk *= 2;
     }
     const int splits = gb_div_up(span, chunk);
-    if (splits > 1 && (long long)n * H * splits <= gb_sink_attention_workspace_rows()) {
+    if (splits > 1 && (long long)n * H * maps * splits <= gb_sink_attention_workspace_rows()) {
       p.splits = splits;
       p.chunk = chunk;
     }
   }
-  const dim3 grid(tiles, G, p.splits);
+  const dim3 grid(tiles, G * maps, p.splits);
   int rc;
 #define TC(DK, DV) rc = narrow ? launch_tc<DK, DV, true>(p, grid, ctx->stream) : launch_tc<DK, DV, false>(p, grid, ctx->stream)
 #define TC_DV(DK)                                                                                    \
@@ -438,6 +458,7 @@ GB_OP(gb_op_sink_attention_tc) {
 #undef TC
   if (rc < 0) return rc;
   if (p.splits == 1) return 1;
-  rc = gb_sink_attention_merge(p.ws, p.splits, p.gate, p.ld_gate, p.out, 1, p.ldo, n, H, vdim, p.sink, ctx->stream);
+  rc = gb_sink_attention_merge(p.ws, p.splits, p.gate, p.ld_gate, out_f32 ? (void*)p.out_f32 : (void*)p.out, out_f32 ? 0 : 1,
+                               p.ldo, n, H * maps, vdim, p.sink, ctx->stream);
   return rc < 0 ? rc : 2;
 }

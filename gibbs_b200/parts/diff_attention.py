@@ -36,11 +36,17 @@ from .position import stretched_inv_freq
 from .runner import BranchPart, Runner, keep
 
 MAPS = 2
+USE_TENSOR_CORES = True          # (the tests switch it off to compare the two kernels)
 
 
 def _workspace_rows() -> int:
     from ..ops.library import library
     return int(library(hybrid.LIBRARY).gb_sink_attention_workspace_rows())
+
+
+def _tensor_cores_take(heads: int, kv_heads: int, dim: int, vdim: int) -> bool:
+    from ..ops.library import library
+    return bool(library(hybrid.LIBRARY).gb_sink_attention_tc_supported(heads, kv_heads, dim, vdim))
 
 
 class DifferentialAttention(BranchPart, Mixer):
@@ -122,18 +128,28 @@ class DifferentialAttention(BranchPart, Mixer):
         rn.linear(h, self.fused, self.fused_bias, fused, role="qkv")
         table, bt_stride = rn.table(kv)
         pages_bf16 = kp.dtype == torch.bfloat16
-        q = rn.buffer("da_query", H * MAPS * dim, torch.float32)
+        # bfloat16 pages and sizes the tensor-core kernel is built for: queries in bfloat16 as well; the maps'
+        # outputs stay 32-bit either way, for the combination behind them
+        tc = pages_bf16 and self.rt.dtype == torch.bfloat16 and USE_TENSOR_CORES and _tensor_cores_take(H, G, dim, vdim)
+        q = rn.buffer("da_query", H * MAPS * dim, torch.bfloat16 if tc else torch.float32)
         rn.op("qk_prep", [fused.data_ptr(), fused.stride(0), self.k_col, self.v_col, keep(rn, self.q_gain),
                           keep(rn, self.k_gain), keep(rn, self.inv_freq), self.rot_dims, rn.tok_req, rn.tok_pos, table,
                           bt_stride, kv.page_size, keep(rn, kp), keep(rn, vp), kp.shape[0], rn.N, H, G, dim, vdim,
                           q.data_ptr(), MAPS], [self.eps],
-              flags=(8 if self.head_norm else 0) | 16 | (4 if pages_bf16 else 0))
+              flags=(8 if self.head_norm else 0) | 16 | (4 if pages_bf16 else 0) | (2 if tc else 0))
         maps_out = rn.buffer("da_maps_out", H * MAPS * vdim, torch.float32)
         ws = rn.buffer("ga_partial", vdim + 2, torch.float32, fixed_rows=_workspace_rows())
-        rn.op("sink_attention", [q.data_ptr(), keep(rn, kp), keep(rn, vp), table, bt_stride, kv.page_size, kp.shape[0],
-                                 rn.tok_req, rn.tok_pos, 0, 0, maps_out.data_ptr(), maps_out.stride(0), rn.N, H, G, dim,
-                                 vdim, self.mask_size, rn.max_context, ws.data_ptr(), MAPS], [self.scale, 0.0],
-              label="diff_attention", flags=(4 if pages_bf16 else 0) | (16 if self.mask_kind == "blocks" else 0))
+        if tc:
+            rn.op("sink_attention_tc", [q.data_ptr(), keep(rn, kp), keep(rn, vp), table, bt_stride, kv.page_size,
+                                        kp.shape[0], rn.tok_req, rn.tok_pos, 0, 0, maps_out.data_ptr(), maps_out.stride(0),
+                                        rn.N, H, G, dim, vdim, self.mask_size, rn.max_context, ws.data_ptr(), rn.R,
+                                        rn.q_start], [self.scale, 0.0], label="diff_attention",
+                  flags=2 | (4 if self.mask_kind == "blocks" else 0) | (MAPS << 8))
+        else:
+            rn.op("sink_attention", [q.data_ptr(), keep(rn, kp), keep(rn, vp), table, bt_stride, kv.page_size, kp.shape[0],
+                                     rn.tok_req, rn.tok_pos, 0, 0, maps_out.data_ptr(), maps_out.stride(0), rn.N, H, G, dim,
+                                     vdim, self.mask_size, rn.max_context, ws.data_ptr(), MAPS], [self.scale, 0.0],
+                  label="diff_attention", flags=(4 if pages_bf16 else 0) | (16 if self.mask_kind == "blocks" else 0))
         heads_out = rn.buffer("da_heads_out", H * vdim)
         rn.op("head_norm", [maps_out.data_ptr(), maps_out.stride(0), MAPS * vdim, maps_out.data_ptr() + 4 * vdim, 0, 0, 0,
                             heads_out.data_ptr(), ops.dtype_code(heads_out.dtype), heads_out.stride(0), rn.N, H, vdim],

@@ -209,9 +209,10 @@ def _matters(fn, h, hot, query):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("decoded", [False, True])
+@pytest.mark.parametrize("vdim", [8, 32])                     # 32: in bfloat16 the tensor-core kernel runs
 @pytest.mark.parametrize("block,T,hot,query", POINTED)
-def test_differential_attention_finds_the_one_key_that_matters(block, T, hot, query, decoded, dtype):
-    m, W, h = _pointed_differential(block, T, hot, query)
+def test_differential_attention_finds_the_one_key_that_matters(block, T, hot, query, vdim, decoded, dtype):
+    m, W, h = _pointed_differential(block, T, hot, query, vdim)
     cfg = one_layer("attention", m, h.shape[1])
     fn = lambda x: plain.differential_attention(x.double(), dbl(W), m, 1e-5)
     want = fn(h)
@@ -223,8 +224,11 @@ def test_differential_attention_finds_the_one_key_that_matters(block, T, hot, qu
     hz = PartHarness(part, n_pages=32, page_size=16)
     got = hz.run_cut("r", h, [query - 10, 1] if decoded else [T])
     e = rel_rows(got, want)
-    assert e[query] <= TOL[dtype], f"query row differs by {e[query]:.3g}"
-    assert e.max() <= (TOL[dtype] if dtype == "float32" else 0.1)
+    # (scores eight times as wide as a model's: where no key stands out, the rounding of keys and queries to
+    # bfloat16 shows in the sharp softmax)
+    loose = TOL[dtype] if dtype == "float32" else 0.1
+    assert e[query] <= (TOL[dtype] if visible else loose), f"query row differs by {e[query]:.3g}"
+    assert e.max() <= loose
 
 
 def _pointed_latent(T, hot, query, seed=11):
@@ -312,6 +316,33 @@ def test_batches_of_unequal_requests_through_one_mixer(dtype):
         for rid in hs:
             assert at[rid] == hs[rid].shape[0]
             check_rows(torch.cat(got[rid], 0), want[rid], dtype, what=f"layer {layer}, {rid}")
+
+
+# (three query heads a kv head, keys of 32 and values of 96 entries, blocks of 50: no multiple of a page or key tile)
+CFG_TC = one_layer("attention", att(6, 2, 32, 96, 0.2, 0.4, block=50, rot=(1000.0, 16), scaling=(4.0, 1.0, 4.0, 64)), 96)
+
+
+@pytest.mark.parametrize("cfg,layer", [(CFG_D, 0), (CFG_D, 4), (CFG_TC, 0)])
+def test_tensor_core_attention_against_the_generic_kernel(cfg, layer, monkeypatch):
+    """bfloat16: the two kernels read the same pages; the tensor-core one reads the queries in bfloat16 too.
+    Whole, cut at odd places (tiles that straddle blocks) and decoded."""
+    from gibbs_b200.parts import diff_attention
+    W = make_weights(cfg, 5)
+    T = 300
+    h = bf(torch.randn(T, cfg["width"], generator=gen(6)))
+    want = plain_mixer(cfg, layer, W, h)
+    outs = {}
+    for tc in (True, False):
+        monkeypatch.setattr(diff_attention, "USE_TENSOR_CORES", tc)
+        part = part_of(cfg, layer, W, "bfloat16")
+        hz = PartHarness(part, n_pages=24, page_size=16)
+        for rid, cuts in (("whole", [T]), ("cut", [37, 2, 90, 1, 1, 64, 5]), ("decoded", [T - 40, 1])):
+            outs[(tc, rid)] = hz.run_cut(rid, h, cuts)
+            check_rows(outs[(tc, rid)], want, "bfloat16", what=f"tensor cores {tc}, {rid}")
+            hz.close(rid)
+    for rid in ("whole", "cut", "decoded"):
+        assert not torch.equal(outs[(True, rid)], outs[(False, rid)])          # (two kernels did run)
+        assert rel_rows(outs[(True, rid)], outs[(False, rid)]).max() < 2e-2
 
 
 # ---------------------------------------------------------------------------
