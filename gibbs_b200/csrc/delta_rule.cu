@@ -111,6 +111,132 @@ delta_scan_kernel(const float* qk, long long ld_qk, int k_col, int v_col, const 
     if (i < dim) S[(size_t)i * vdim] = s[i];
 }
 
+// The same recurrence with a column of S shared by SPLIT neighbouring lanes, each with PER of the column's dim
+// values (dim <= SPLIT * PER), so a token costs a thread 4 PER operations and the column 2 log2(SPLIT) shuffles;
+// q, k and the decays are read from shared memory four values an instruction.  The inputs of TOK tokens at a
+// time (q, k, decay, the block's columns of v, beta) arrive by asynchronous copies into one of two buffers
+// while the tokens of the other are consumed, so the recurrence itself reads nothing from global memory.
+// The sums over dim run in another order than in the kernel above; which of the two runs depends on the
+// layer's sizes only.
+constexpr int DCOL_THREADS = 64;
+
+__device__ __forceinline__ void dcol_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int LEFT> __device__ __forceinline__ void dcol_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(LEFT) : "memory");
+}
+
+template <int SPLIT, int PER, int TOK>
+__global__ void __launch_bounds__(DCOL_THREADS)
+delta_scan_cols_kernel(const float* qk, long long ld_qk, int k_col, int v_col, const float* decay, long long ld_g,
+                       const float* beta, float* state, long long slot_stride, const int* slot_ids, const int* q_start,
+                       const int* q_len, float* out, long long ldo, int H, int G, int dim, int vdim) {
+  constexpr int NR = SPLIT * PER, COLS = DCOL_THREADS / SPLIT, Q4 = PER / 4;
+  constexpr int BUF = TOK * (3 * NR + COLS) + ((TOK + 3) & ~3);   // q [TOK][NR] | k | decay | v [TOK][COLS] | beta [TOK]
+  extern __shared__ __align__(16) float dcol[];                   // [2][BUF]
+  pdl_trigger();
+  const int col = threadIdx.x / SPLIT, q = threadIdx.x % SPLIT;
+  const int r = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * COLS, c = c0 + col;
+  const bool active = c < vdim;
+  const int g = h / (H / G);
+  const int first = q_start[r], len = q_len[r];
+  float* S = state + (size_t)slot_ids[r] * slot_stride + (size_t)h * dim * vdim + (active ? c : 0);
+  if (dim < NR)                                                   // the padding dim .. NR of q, k and decay stays zero
+    for (int i = threadIdx.x; i < 2 * BUF; i += DCOL_THREADS) dcol[i] = 0.f;
+  pdl_wait();
+  // this thread's rows of the column: n = 4 (q + SPLIT i) + e, i < Q4, e < 4
+  float s[PER];
+#pragma unroll
+  for (int i = 0; i < Q4; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int n = 4 * (q + SPLIT * i) + e;
+      s[4 * i + e] = (active && n < dim) ? S[(size_t)n * vdim] : 0.f;
+    }
+  __syncthreads();
+
+  const int pieces = dim >> 2, vpieces = min(COLS, vdim - c0) >> 2;
+  auto stage = [&](int t0, int b) {
+    const int nt = min(TOK, len - t0);
+    float* Q = dcol + b * BUF;
+    float* V = Q + 3 * TOK * NR;
+    for (int i = threadIdx.x; i < 3 * nt * pieces; i += DCOL_THREADS) {
+      const int which = i / (nt * pieces), rem = i - which * nt * pieces;
+      const int tt = rem / pieces, c4 = rem - tt * pieces;
+      const size_t row = (size_t)(first + t0 + tt);
+      const float* src = which == 2 ? decay + row * ld_g + h * dim + 4 * c4
+                                    : qk + row * ld_qk + (which ? k_col : 0) + g * dim + 4 * c4;
+      gb_cp_async_16(Q + (which * TOK + tt) * NR + 4 * c4, src);
+    }
+    for (int i = threadIdx.x; i < nt * vpieces; i += DCOL_THREADS) {
+      const int tt = i / vpieces, c4 = i - tt * vpieces;
+      gb_cp_async_16(V + tt * COLS + 4 * c4, qk + (size_t)(first + t0 + tt) * ld_qk + v_col + h * vdim + c0 + 4 * c4);
+    }
+    if ((int)threadIdx.x < nt)
+      gb_cp_async_4(V + TOK * COLS + threadIdx.x, beta + (size_t)(first + t0 + threadIdx.x) * H + h);
+    dcol_commit();
+  };
+
+  if (len > 0) stage(0, 0);
+  int b = 0;
+  for (int t0 = 0; t0 < len; t0 += TOK, b ^= 1) {
+    const int nt = min(TOK, len - t0);
+    if (t0 + TOK < len) {
+      stage(t0 + TOK, b ^ 1);
+      dcol_wait<1>();                                             // this chunk has landed, the next is on its way
+    } else {
+      dcol_wait<0>();
+    }
+    __syncthreads();
+    const float* Q = dcol + b * BUF;
+    const float* K = Q + TOK * NR;
+    const float* Gd = K + TOK * NR;
+    const float* V = Gd + TOK * NR;
+    const float* Bt = V + TOK * COLS;
+#pragma unroll 2
+    for (int tt = 0; tt < nt; ++tt) {                             // (every lane, also of a column beyond vdim: the shuffles)
+      const float v = active ? V[tt * COLS + col] : 0.f, bt = Bt[tt];
+      float4 k4[Q4];
+      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;               // four chains, added in a fixed order
+#pragma unroll
+      for (int i = 0; i < Q4; ++i) {
+        const float4 g4 = *reinterpret_cast<const float4*>(Gd + tt * NR + 4 * (q + SPLIT * i));
+        k4[i] = *reinterpret_cast<const float4*>(K + tt * NR + 4 * (q + SPLIT * i));
+        s[4 * i] *= g4.x;         d0 = fmaf(s[4 * i], k4[i].x, d0);
+        s[4 * i + 1] *= g4.y;     d1 = fmaf(s[4 * i + 1], k4[i].y, d1);
+        s[4 * i + 2] *= g4.z;     d2 = fmaf(s[4 * i + 2], k4[i].z, d2);
+        s[4 * i + 3] *= g4.w;     d3 = fmaf(s[4 * i + 3], k4[i].w, d3);
+      }
+      float dot = (d0 + d1) + (d2 + d3);
+#pragma unroll
+      for (int o = 1; o < SPLIT; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      const float u = bt * (v - dot);
+      d0 = d1 = d2 = d3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < Q4; ++i) {
+        const float4 q4 = *reinterpret_cast<const float4*>(Q + tt * NR + 4 * (q + SPLIT * i));
+        s[4 * i] = fmaf(k4[i].x, u, s[4 * i]);             d0 = fmaf(s[4 * i], q4.x, d0);
+        s[4 * i + 1] = fmaf(k4[i].y, u, s[4 * i + 1]);     d1 = fmaf(s[4 * i + 1], q4.y, d1);
+        s[4 * i + 2] = fmaf(k4[i].z, u, s[4 * i + 2]);     d2 = fmaf(s[4 * i + 2], q4.z, d2);
+        s[4 * i + 3] = fmaf(k4[i].w, u, s[4 * i + 3]);     d3 = fmaf(s[4 * i + 3], q4.w, d3);
+      }
+      float o = (d0 + d1) + (d2 + d3);
+#pragma unroll
+      for (int w = 1; w < SPLIT; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+      if (active && q == 0) out[(size_t)(first + t0 + tt) * ldo + h * vdim + c] = o;
+    }
+    __syncthreads();                                              // before the copies of the chunk after next land here
+  }
+  if (active) {
+#pragma unroll
+    for (int i = 0; i < Q4; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int n = 4 * (q + SPLIT * i) + e;
+        if (n < dim) S[(size_t)n * vdim] = s[4 * i + e];
+      }
+  }
+}
+
 }  // namespace
 
 // a0 rows [q (kv_heads * dim) | k (kv_heads * dim) | v] after the convolution (f32, changed in place), a1 their
@@ -133,12 +259,31 @@ GB_OP(gb_op_delta_prep) {
 // a4 decays [tokens, heads * dim] (f32), a5 their row stride, a6 beta [tokens, heads] (f32), a7 recurrent state of
 // slot 0 ([heads][dim][vdim], f32), a8 elements between slots, a9 slot ids, a10 first row per request, a11 rows per
 // request, a12 out [tokens, heads * vdim] (f32), a13 its row stride, a14 requests, a15 heads, a16 kv heads, a17 dim,
-// a18 vdim
+// a18 vdim; flags bit 0: the kernel with one thread a column, whatever the sizes
 GB_OP(gb_op_delta_scan) {
   const int R = (int)a[14], H = (int)a[15], G = (int)a[16], dim = (int)a[17], vdim = (int)a[18];
   if (R <= 0) return 0;
   if (G <= 0 || H % G) GB_FAIL(GB_ERR_ARG, "delta_scan: %d heads over %d key heads", H, G);
   if (dim > 256) GB_FAIL(GB_ERR_ARG, "delta_scan: keys of %d entries (at most 256)", dim);
+  // rows that can be copied in 16-byte pieces: a column of S over several lanes, inputs staged ahead
+  if (!(flags & 1) && dim % 4 == 0 && vdim % 4 == 0 && a[1] % 4 == 0 && a[2] % 4 == 0 && a[3] % 4 == 0 && a[5] % 4 == 0 &&
+      (a[0] & 15) == 0 && (a[4] & 15) == 0) {
+#define COLS_SCAN(SPLIT, PER, TOK)                                                                                      \
+    gb_launch(delta_scan_cols_kernel<SPLIT, PER, TOK>, dim3(R, H, gb_div_up(vdim, DCOL_THREADS / SPLIT)),                \
+              dim3(DCOL_THREADS),                                                                                       \
+              sizeof(float) * 2 * ((size_t)TOK * (3 * SPLIT * PER + DCOL_THREADS / SPLIT) + ((TOK + 3) & ~3)),          \
+              ctx->stream, op_ptr<const float>(a[0]), a[1], (int)a[2], (int)a[3], op_ptr<const float>(a[4]), a[5],       \
+              op_ptr<const float>(a[6]), op_ptr<float>(a[7]), a[8], op_ptr<const int>(a[9]), op_ptr<const int>(a[10]),   \
+              op_ptr<const int>(a[11]), op_ptr<float>(a[12]), a[13], H, G, dim, vdim)
+    if (dim <= 16) COLS_SCAN(1, 16, 16);
+    else if (dim <= 32) COLS_SCAN(2, 16, 16);
+    else if (dim <= 64) COLS_SCAN(4, 16, 16);
+    else if (dim <= 128) COLS_SCAN(8, 16, 8);
+    else COLS_SCAN(8, 32, 4);
+#undef COLS_SCAN
+    GB_CHECK_LAUNCH("delta_scan (columns)");
+    return 1;
+  }
   const size_t smem = sizeof(float) * 3 * DS_TOKENS * (size_t)dim;
 #define SCAN(DK, COLS)                                                                                                  \
   gb_launch(delta_scan_kernel<DK, COLS>, dim3(R, H, gb_div_up(vdim, COLS)), dim3(COLS), smem, ctx->stream,               \

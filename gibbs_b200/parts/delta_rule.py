@@ -26,6 +26,8 @@ from ..ops import hybrid
 from .base import Mixer, SlotState, TensorDecl, VECTOR, register_part
 from .runner import BranchPart, Runner, keep
 
+SPLIT_COLUMNS = True             # (the tests switch it off to compare the recurrence's two kernels)
+
 
 class GatedDeltaRule(BranchPart, Mixer):
     adds_in_place = True
@@ -92,7 +94,7 @@ class GatedDeltaRule(BranchPart, Mixer):
         y = rn.buffer("dr_out", H * vdim, torch.float32)
         rn.op("delta_scan", [qkv.data_ptr(), qkv.stride(0), G * dim, 2 * G * dim, a.data_ptr(), a.stride(0),
                              beta.data_ptr(), keep(rn, rec.state), rec.state.stride(0), slots, rn.q_start, rn.q_len,
-                             y.data_ptr(), y.stride(0), rn.R, H, G, dim, vdim])
+                             y.data_ptr(), y.stride(0), rn.R, H, G, dim, vdim], flags=0 if SPLIT_COLUMNS else 1)
         o = rn.buffer("dr_heads_out", H * vdim)
         rn.op("head_norm", [y.data_ptr(), y.stride(0), vdim, 0, keep(rn, self.gain), gate.data_ptr(), gate.stride(0),
                             o.data_ptr(), ops.dtype_code(o.dtype), o.stride(0), rn.N, H, vdim], [self.eps, 0.0, 1.0],

@@ -345,6 +345,31 @@ def test_tensor_core_attention_against_the_generic_kernel(cfg, layer, monkeypatc
         assert rel_rows(outs[(True, rid)], outs[(False, rid)]).max() < 2e-2
 
 
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(2, 1, 4, 4), (3, 3, 12, 20), (2, 2, 20, 72), (4, 2, 32, 8), (2, 1, 48, 36),
+                                                     (4, 1, 64, 64), (1, 1, 100, 12), (2, 1, 128, 40), (1, 1, 160, 16),
+                                                     (2, 2, 256, 24)])
+def test_delta_rule_with_split_columns_against_one_thread_a_column(heads, kv_heads, dim, vdim, monkeypatch):
+    """32-bit: every size class of the kernel that spreads a column of the state over several lanes, against the
+    plain recurrence and against the kernel with one thread a column.  Whole, cut and decoded, two slots."""
+    from gibbs_b200.parts import delta_rule
+    cfg = one_layer("channel_delta", delta(heads, kv_heads, dim, vdim, 3, 4, 4), 48)
+    W = make_weights(cfg, 9)
+    T = 90
+    h = bf(torch.randn(T, 48, generator=gen(10)))
+    want = plain_mixer(cfg, 0, W, h)
+    outs = {}
+    for split in (True, False):
+        monkeypatch.setattr(delta_rule, "SPLIT_COLUMNS", split)
+        part = part_of(cfg, 0, W, "float32")
+        hz = PartHarness(part, n_slots=2)
+        for rid, cuts in (("whole", [T]), ("cut", [2, 15, 1, 16, 17, 2, 33, 4]), ("decoded", [T - 40, 1])):
+            outs[(split, rid)] = hz.run_cut(rid, h, cuts)
+            check_rows(outs[(split, rid)], want, "float32", what=f"split {split}, {rid}")
+            hz.close(rid)
+    for rid in ("whole", "cut", "decoded"):
+        assert rel_rows(outs[(True, rid)], outs[(False, rid)]).max() < 1e-5
+
+
 # ---------------------------------------------------------------------------
 # whole models through the engine
 # ---------------------------------------------------------------------------
