@@ -362,6 +362,7 @@ __global__ void latent_attention_merge_kernel(const float* ws, int splits, const
       const float e = m > -INFINITY ? expf(m - M) : 0.f;
       for (int u = 0; u < 32 && s0 + u < splits; ++u) {
         const float eu = __shfl_sync(0xffffffffu, e, u);
+        if (eu == 0.f) continue;                             // a chunk without keys (the whole warp together)
         const float* wu = w + (size_t)(s0 + u) * (r + 2) + 2;
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
@@ -396,8 +397,8 @@ GB_API int gb_latent_attention_chunks(int n, int H, int window, int max_ctx, int
     chunk = 32 * gb_div_up(gb_div_up(span, wanted), 32);
     if (chunk < 32) chunk = 32;
   } else {
-    chunk = 256;
-    while (gb_div_up(span, chunk) > 2 * wanted) chunk *= 2;
+    chunk = 2 * LA_KT;
+    while (gb_div_up(span, chunk) > wanted) chunk *= 2;
   }
   *chunk_out = chunk;
   return gb_div_up(span, chunk);
