@@ -227,6 +227,29 @@ __global__ void act_rows_kernel(const float* x, long long ld, TO* out, long long
   out[(size_t)t * ldo + c] = from_f32<TO>(act_value(x[(size_t)t * ld + c], kind));
 }
 
+// Four neighbouring values a thread (rows that can be read and written in whole pieces of four); the same
+// arithmetic per value as above.
+template <typename TO>
+__global__ void act_rows4_kernel(const float* x, long long ld, TO* out, long long ldo, int n, int inner4, int kind) {
+  pdl_trigger();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)n * inner4) return;
+  const int t = (int)(i / inner4), c = 4 * (int)(i - (long long)t * inner4);
+  const float4 v = *reinterpret_cast<const float4*>(x + (size_t)t * ld + c);
+  const float r0 = act_value(v.x, kind), r1 = act_value(v.y, kind), r2 = act_value(v.z, kind), r3 = act_value(v.w, kind);
+  TO* o = out + (size_t)t * ldo + c;
+  if constexpr (sizeof(TO) == 2) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(r0, r1), hi = __floats2bfloat162_rn(r2, r3);
+    uint2 w;
+    w.x = *reinterpret_cast<unsigned*>(&lo);
+    w.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(o) = w;
+  } else {
+    *reinterpret_cast<float4*>(o) = make_float4(r0, r1, r2, r3);
+  }
+}
+
 // one warp per (row, head); values of up to 32 * HN_VR entries stay in registers
 constexpr int HN_VR = 8;
 
@@ -368,6 +391,18 @@ GB_OP(gb_op_act_rows) {
   const int n = (int)a[5], inner = (int)a[6];
   if (n <= 0) return 0;
   if (a[7] > ACT_RELU) GB_FAIL(GB_ERR_ARG, "act_rows: function %lld", a[7]);
+  const size_t out_bytes = a[3] == GB_BF16 ? 2 : 4;
+  if (inner % 4 == 0 && a[1] % 4 == 0 && a[4] % 4 == 0 && (a[0] & 15) == 0 && (a[2] & (4 * out_bytes - 1)) == 0) {
+    const dim3 grid4(gb_div_up((long long)n * (inner / 4), 256)), block4(256);
+    if (a[3] == GB_BF16)
+      gb_launch(act_rows4_kernel<bf16>, grid4, block4, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], op_ptr<bf16>(a[2]),
+                a[4], n, inner / 4, (int)a[7]);
+    else
+      gb_launch(act_rows4_kernel<float>, grid4, block4, 0, ctx->stream, op_ptr<const float>(a[0]), a[1],
+                op_ptr<float>(a[2]), a[4], n, inner / 4, (int)a[7]);
+    GB_CHECK_LAUNCH("act_rows (four a thread)");
+    return 1;
+  }
   const dim3 grid(gb_div_up((long long)n * inner, 256)), block(256);
   if (a[3] == GB_BF16)
     gb_launch(act_rows_kernel<bf16>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], op_ptr<bf16>(a[2]), a[4],
