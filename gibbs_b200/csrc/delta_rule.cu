@@ -12,8 +12,9 @@
 //  gb_op_delta_prep   what enters the recurrence, per token, all in 32-bit: q and k (after their short
 //                     convolution) become unit vectors per head, x / sqrt(sum x^2 + unit_eps), q also times
 //                     q_scale; beta = sigmoid(b); g = exp(-exp(A_log[h]) * softplus(a + dt_bias))
-//  gb_op_delta_scan   the recurrence; one thread owns one column of S (dim values in registers), so the two
-//                     products with S are sums inside a thread and need no exchange
+//  gb_op_delta_scan   the recurrence; a column of S (dim values) lives in the registers of one thread, or,
+//                     where rows can be copied in 16-byte pieces, of up to 16 neighbouring lanes that add
+//                     their shares of the two products with S by shuffles
 //
 // State layout in a slot: [heads][dim][vdim].
 #include "hybrid.cuh"
@@ -154,22 +155,42 @@ delta_scan_cols_kernel(const float* qk, long long ld_qk, int k_col, int v_col, c
     }
   __syncthreads();
 
+  // What a thread copies is the same for every token: 16-byte piece number threadIdx.x (+ 64, ...) of a token's
+  // [q | k | decay | this block's columns of v]; source, row stride and place in the buffer are worked out once.
   const int pieces = dim >> 2, vpieces = min(COLS, vdim - c0) >> 2;
+  constexpr int ROLES = (3 * NR / 4 + COLS / 4 + DCOL_THREADS - 1) / DCOL_THREADS;
+  const float* r_src[ROLES];
+  long long r_ld[ROLES];
+  int r_dst[ROLES], r_step[ROLES];
+#pragma unroll
+  for (int j = 0; j < ROLES; ++j) {
+    const int i = threadIdx.x + j * DCOL_THREADS;
+    r_src[j] = nullptr;
+    r_ld[j] = 0;
+    r_dst[j] = r_step[j] = 0;
+    if (i < 3 * pieces) {
+      const int which = i / pieces, c4 = i - which * pieces;
+      r_src[j] = which == 2 ? decay + (size_t)first * ld_g + h * dim + 4 * c4
+                            : qk + (size_t)first * ld_qk + (which ? k_col : 0) + g * dim + 4 * c4;
+      r_ld[j] = which == 2 ? ld_g : ld_qk;
+      r_dst[j] = which * TOK * NR + 4 * c4;
+      r_step[j] = NR;
+    } else if (i < 3 * pieces + vpieces) {
+      const int c4 = i - 3 * pieces;
+      r_src[j] = qk + (size_t)first * ld_qk + v_col + h * vdim + c0 + 4 * c4;
+      r_ld[j] = ld_qk;
+      r_dst[j] = 3 * TOK * NR + 4 * c4;
+      r_step[j] = COLS;
+    }
+  }
   auto stage = [&](int t0, int b) {
     const int nt = min(TOK, len - t0);
     float* Q = dcol + b * BUF;
     float* V = Q + 3 * TOK * NR;
-    for (int i = threadIdx.x; i < 3 * nt * pieces; i += DCOL_THREADS) {
-      const int which = i / (nt * pieces), rem = i - which * nt * pieces;
-      const int tt = rem / pieces, c4 = rem - tt * pieces;
-      const size_t row = (size_t)(first + t0 + tt);
-      const float* src = which == 2 ? decay + row * ld_g + h * dim + 4 * c4
-                                    : qk + row * ld_qk + (which ? k_col : 0) + g * dim + 4 * c4;
-      gb_cp_async_16(Q + (which * TOK + tt) * NR + 4 * c4, src);
-    }
-    for (int i = threadIdx.x; i < nt * vpieces; i += DCOL_THREADS) {
-      const int tt = i / vpieces, c4 = i - tt * vpieces;
-      gb_cp_async_16(V + tt * COLS + 4 * c4, qk + (size_t)(first + t0 + tt) * ld_qk + v_col + h * vdim + c0 + 4 * c4);
+    for (int tt = 0; tt < nt; ++tt) {
+#pragma unroll
+      for (int j = 0; j < ROLES; ++j)
+        if (r_src[j]) gb_cp_async_16(Q + r_dst[j] + tt * r_step[j], r_src[j] + (size_t)(t0 + tt) * r_ld[j]);
     }
     if ((int)threadIdx.x < nt)
       gb_cp_async_4(V + TOK * COLS + threadIdx.x, beta + (size_t)(first + t0 + threadIdx.x) * H + h);
@@ -192,38 +213,63 @@ delta_scan_cols_kernel(const float* qk, long long ld_qk, int k_col, int v_col, c
     const float* Gd = K + TOK * NR;
     const float* V = Gd + TOK * NR;
     const float* Bt = V + TOK * COLS;
+    // A warp issues in order and is alone on its scheduler, so what does not depend on the token's chain is
+    // placed where the chain waits: token tt + 1's operands are read from shared memory while token tt is
+    // computed, and token tt's read-out is summed over the lanes and stored while token tt + 1's chain runs.
+    float4 g4[Q4], k4[Q4], q4[Q4];
+#pragma unroll
+    for (int i = 0; i < Q4; ++i) {
+      g4[i] = *reinterpret_cast<const float4*>(Gd + 4 * (q + SPLIT * i));
+      k4[i] = *reinterpret_cast<const float4*>(K + 4 * (q + SPLIT * i));
+      q4[i] = *reinterpret_cast<const float4*>(Q + 4 * (q + SPLIT * i));
+    }
+    float v = active ? V[col] : 0.f, bt = Bt[0];
+    float o_before = 0.f;                                         // token tt - 1's read-out, this lane's share
 #pragma unroll 2
     for (int tt = 0; tt < nt; ++tt) {                             // (every lane, also of a column beyond vdim: the shuffles)
-      const float v = active ? V[tt * COLS + col] : 0.f, bt = Bt[tt];
-      float4 k4[Q4];
+      const int tn = min(tt + 1, nt - 1);
+      float4 g4n[Q4], k4n[Q4], q4n[Q4];
+#pragma unroll
+      for (int i = 0; i < Q4; ++i) {
+        g4n[i] = *reinterpret_cast<const float4*>(Gd + tn * NR + 4 * (q + SPLIT * i));
+        k4n[i] = *reinterpret_cast<const float4*>(K + tn * NR + 4 * (q + SPLIT * i));
+        q4n[i] = *reinterpret_cast<const float4*>(Q + tn * NR + 4 * (q + SPLIT * i));
+      }
+      const float vn = active ? V[tn * COLS + col] : 0.f, btn = Bt[tn];
       float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;               // four chains, added in a fixed order
 #pragma unroll
       for (int i = 0; i < Q4; ++i) {
-        const float4 g4 = *reinterpret_cast<const float4*>(Gd + tt * NR + 4 * (q + SPLIT * i));
-        k4[i] = *reinterpret_cast<const float4*>(K + tt * NR + 4 * (q + SPLIT * i));
-        s[4 * i] *= g4.x;         d0 = fmaf(s[4 * i], k4[i].x, d0);
-        s[4 * i + 1] *= g4.y;     d1 = fmaf(s[4 * i + 1], k4[i].y, d1);
-        s[4 * i + 2] *= g4.z;     d2 = fmaf(s[4 * i + 2], k4[i].z, d2);
-        s[4 * i + 3] *= g4.w;     d3 = fmaf(s[4 * i + 3], k4[i].w, d3);
+        s[4 * i] *= g4[i].x;         d0 = fmaf(s[4 * i], k4[i].x, d0);
+        s[4 * i + 1] *= g4[i].y;     d1 = fmaf(s[4 * i + 1], k4[i].y, d1);
+        s[4 * i + 2] *= g4[i].z;     d2 = fmaf(s[4 * i + 2], k4[i].z, d2);
+        s[4 * i + 3] *= g4[i].w;     d3 = fmaf(s[4 * i + 3], k4[i].w, d3);
       }
       float dot = (d0 + d1) + (d2 + d3);
+      float ob = o_before;
 #pragma unroll
-      for (int o = 1; o < SPLIT; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      for (int w = 1; w < SPLIT; w <<= 1) {
+        dot += __shfl_xor_sync(0xffffffffu, dot, w);
+        ob += __shfl_xor_sync(0xffffffffu, ob, w);
+      }
+      if (active && q == 0 && tt > 0) out[(size_t)(first + t0 + tt - 1) * ldo + h * vdim + c] = ob;
       const float u = bt * (v - dot);
       d0 = d1 = d2 = d3 = 0.f;
 #pragma unroll
       for (int i = 0; i < Q4; ++i) {
-        const float4 q4 = *reinterpret_cast<const float4*>(Q + tt * NR + 4 * (q + SPLIT * i));
-        s[4 * i] = fmaf(k4[i].x, u, s[4 * i]);             d0 = fmaf(s[4 * i], q4.x, d0);
-        s[4 * i + 1] = fmaf(k4[i].y, u, s[4 * i + 1]);     d1 = fmaf(s[4 * i + 1], q4.y, d1);
-        s[4 * i + 2] = fmaf(k4[i].z, u, s[4 * i + 2]);     d2 = fmaf(s[4 * i + 2], q4.z, d2);
-        s[4 * i + 3] = fmaf(k4[i].w, u, s[4 * i + 3]);     d3 = fmaf(s[4 * i + 3], q4.w, d3);
+        s[4 * i] = fmaf(k4[i].x, u, s[4 * i]);             d0 = fmaf(s[4 * i], q4[i].x, d0);
+        s[4 * i + 1] = fmaf(k4[i].y, u, s[4 * i + 1]);     d1 = fmaf(s[4 * i + 1], q4[i].y, d1);
+        s[4 * i + 2] = fmaf(k4[i].z, u, s[4 * i + 2]);     d2 = fmaf(s[4 * i + 2], q4[i].z, d2);
+        s[4 * i + 3] = fmaf(k4[i].w, u, s[4 * i + 3]);     d3 = fmaf(s[4 * i + 3], q4[i].w, d3);
       }
-      float o = (d0 + d1) + (d2 + d3);
+      o_before = (d0 + d1) + (d2 + d3);
 #pragma unroll
-      for (int w = 1; w < SPLIT; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
-      if (active && q == 0) out[(size_t)(first + t0 + tt) * ldo + h * vdim + c] = o;
+      for (int i = 0; i < Q4; ++i) { g4[i] = g4n[i]; k4[i] = k4n[i]; q4[i] = q4n[i]; }
+      v = vn;
+      bt = btn;
     }
+#pragma unroll
+    for (int w = 1; w < SPLIT; w <<= 1) o_before += __shfl_xor_sync(0xffffffffu, o_before, w);
+    if (active && q == 0) out[(size_t)(first + t0 + nt - 1) * ldo + h * vdim + c] = o_before;
     __syncthreads();                                              // before the copies of the chunk after next land here
   }
   if (active) {
@@ -275,11 +321,12 @@ GB_OP(gb_op_delta_scan) {
               ctx->stream, op_ptr<const float>(a[0]), a[1], (int)a[2], (int)a[3], op_ptr<const float>(a[4]), a[5],       \
               op_ptr<const float>(a[6]), op_ptr<float>(a[7]), a[8], op_ptr<const int>(a[9]), op_ptr<const int>(a[10]),   \
               op_ptr<const int>(a[11]), op_ptr<float>(a[12]), a[13], H, G, dim, vdim)
-    if (dim <= 16) COLS_SCAN(1, 16, 16);
-    else if (dim <= 32) COLS_SCAN(2, 16, 16);
-    else if (dim <= 64) COLS_SCAN(4, 16, 16);
+    if (dim <= 8) COLS_SCAN(1, 8, 16);
+    else if (dim <= 16) COLS_SCAN(2, 8, 16);
+    else if (dim <= 32) COLS_SCAN(4, 8, 16);
+    else if (dim <= 64) COLS_SCAN(8, 8, 16);
     else if (dim <= 128) COLS_SCAN(8, 16, 8);
-    else COLS_SCAN(8, 32, 4);
+    else COLS_SCAN(16, 16, 4);
 #undef COLS_SCAN
     GB_CHECK_LAUNCH("delta_scan (columns)");
     return 1;
