@@ -92,6 +92,58 @@ __global__ void row_norm_kernel(const float* x, long long ldx, const float* __re
   }
 }
 
+// One warp a row, the row in registers as V4 pieces of four values a lane (dim <= 128 * V4, a multiple of 4, rows
+// 16-byte aligned): no block-wide sums, 16-byte loads and packed stores.  Which kernel runs depends on the row's
+// length and alignment only, never on the number of rows.
+template <typename TO, int V4>
+__global__ void __launch_bounds__(128)
+row_norm_warp_kernel(const float* x, long long ldx, const float* __restrict__ gain, TO* out, const int* rows, int n, int dim,
+                     int kind, float eps) {
+  pdl_trigger();
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= n) return;                                     // (whole warps; nothing below meets the block)
+  const int src = rows ? rows[r] : r;
+  pdl_wait();
+  const float* row = x + (size_t)src * ldx;
+  float4 v[V4];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < V4; ++i) {
+    const int d = 4 * (lane + 32 * i);
+    v[i] = d < dim ? *reinterpret_cast<const float4*>(row + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+    s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+  }
+  const float mean = kind == NORM_LAYER ? warp_sum(s) / (float)dim : 0.f;
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < V4; ++i) {
+    if (4 * (lane + 32 * i) < dim) {
+      const float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, e = v[i].w - mean;
+      ss += (a * a + b * b) + (c * c + e * e);
+    }
+  }
+  const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)dim + eps);
+  TO* o = out + (size_t)r * dim;
+#pragma unroll
+  for (int i = 0; i < V4; ++i) {
+    const int d = 4 * (lane + 32 * i);
+    if (d >= dim) continue;
+    const float4 g = *reinterpret_cast<const float4*>(gain + d);
+    const float r0 = (v[i].x - mean) * rstd * g.x, r1 = (v[i].y - mean) * rstd * g.y;
+    const float r2 = (v[i].z - mean) * rstd * g.z, r3 = (v[i].w - mean) * rstd * g.w;
+    if constexpr (sizeof(TO) == 2) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(r0, r1), hi = __floats2bfloat162_rn(r2, r3);
+      uint2 w;
+      w.x = *reinterpret_cast<unsigned*>(&lo);
+      w.y = *reinterpret_cast<unsigned*>(&hi);
+      *reinterpret_cast<uint2*>(o + d) = w;
+    } else {
+      *reinterpret_cast<float4*>(o + d) = make_float4(r0, r1, r2, r3);
+    }
+  }
+}
+
 // `then`: the norm in front of the NEXT sublayer, taken of the new rows while they are in registers
 // (out2 = norm2(x) * gain2), so that it needs no kernel and no second trip of its own.
 struct ThenNorm {
@@ -295,6 +347,23 @@ GB_OP(gb_op_row_norm) {
   const int n = (int)a[6], dim = (int)a[7], kind = (int)a[8];
   if (n <= 0) return 0;
   if (kind != NORM_LAYER && kind != NORM_RMS) GB_FAIL(GB_ERR_ARG, "row_norm: kind %d", kind);
+  const size_t out_bytes = a[4] == GB_BF16 ? 2 : 4;
+  if (dim % 4 == 0 && dim <= 2048 && a[1] % 4 == 0 && (a[0] & 15) == 0 && (a[2] & 15) == 0 && (a[3] & (4 * out_bytes - 1)) == 0) {
+    const dim3 wgrid(gb_div_up(n, 4)), wblock(128);
+#define WARP_NORM(TO, V4)                                                                                               \
+    gb_launch(row_norm_warp_kernel<TO, V4>, wgrid, wblock, 0, ctx->stream, op_ptr<const float>(a[0]), a[1],              \
+              op_ptr<const float>(a[2]), op_ptr<TO>(a[3]), op_ptr<const int>(a[5]), n, dim, kind, (float)f[0])
+#define WARP_NORM_V4(TO)                                                                                                \
+    do {                                                                                                                \
+      if (dim <= 128) WARP_NORM(TO, 1); else if (dim <= 256) WARP_NORM(TO, 2); else if (dim <= 512) WARP_NORM(TO, 4);   \
+      else if (dim <= 1024) WARP_NORM(TO, 8); else WARP_NORM(TO, 16);                                                   \
+    } while (0)
+    if (a[4] == GB_BF16) WARP_NORM_V4(bf16); else WARP_NORM_V4(float);
+#undef WARP_NORM_V4
+#undef WARP_NORM
+    GB_CHECK_LAUNCH("row_norm (a warp a row)");
+    return 1;
+  }
   const dim3 grid(n), block(norm_threads(dim));
   if (a[4] == GB_BF16)
     gb_launch(row_norm_kernel<bf16>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], op_ptr<const float>(a[2]),
