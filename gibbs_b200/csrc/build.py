@@ -31,7 +31,7 @@ LIBRARIES = {
     "runtime": ["errors.cu", "step_plan.cu"],
     # layer norms, clamped gated units, latent and gated attention, state-space and delta-rule recurrences, routed experts: every entry
     # point has the signature of a step-plan operation (hybrid.cuh)
-    "hybrid": ["errors.cu", "norms.cu", "latent_attention.cu", "gated_attention.cu", "gated_attention_tc.cu", "ssm.cu", "delta_rule.cu",
+    "hybrid": ["errors.cu", "norms.cu", "latent_attention.cu", "latent_attention_tc.cu", "gated_attention.cu", "gated_attention_tc.cu", "ssm.cu", "delta_rule.cu",
                "moe.cu", "moe_tc.cu"],
 }
 

@@ -381,6 +381,13 @@ __global__ void latent_attention_merge_kernel(const float* ws, int splits, const
 
 }  // namespace
 
+bool gb_latent_attention_tc_takes(int n, int R, int H, int r, int dr, int window, bool pages_bf16, const void* pages,
+                                  const void* qp, const void* out, long long ldo);
+int gb_latent_attention_tc_launch(const float* qp, const bf16* pages, const int* block_table, int bt_stride, int page_size,
+                                  int n_pages, const int* tok_req, const int* tok_pos, const int* q_start,
+                                  const float* gate, long long ld_gate, float* out, long long ldo, int n, int R, int H, int r,
+                                  float scale, const float* sink, int* status, cudaStream_t stream);
+
 // How the visible keys of a launch are cut into chunks of whole key tiles: (chunks, keys per chunk).
 // Few tokens (decoding) get many chunks, so that the GPU is occupied; a launch with enough (token, head
 // group) blocks of its own gets one.  With a window the chunk depends on the launch's sizes only, not on
@@ -455,10 +462,25 @@ GB_OP(gb_op_head_linear) {
 // 0, a10 that stride, a11 out [tokens, heads * r] (f32), a12 its row stride, a13 tokens, a14 heads, a15 latent size,
 // a16 rotated size, a17 window (0: every earlier position), a18 longest context of the step (an upper bound will do),
 // a19 workspace for partial results, gb_latent_attention_workspace_rows() rows of (latent size + 2) floats, a20 a
-// learned sink score per head (f32 [heads]) whose exponential joins the softmax's denominator, or 0; f0 scale
+// learned sink score per head (f32 [heads]) whose exponential joins the softmax's denominator, or 0; a21 requests of
+// the step, a22 first row per request (requests' rows follow one another in the order of the requests; a22 = 0: the
+// generic kernel whatever the step); f0 scale
 GB_OP(gb_op_latent_attention) {
   const int n = (int)a[13], H = (int)a[14], r = (int)a[15], dr = (int)a[16];
   if (n <= 0) return 0;
+  // a step that carries portions of prompts, bfloat16 pages: the tensor-core kernel (latent_attention_tc.cu)
+  if (a[22] &&
+      gb_latent_attention_tc_takes(n, (int)a[21], H, r, dr, (int)a[17], a[2] == GB_BF16, op_ptr<const void>(a[1]),
+                                   op_ptr<const void>(a[0]), op_ptr<const void>(a[11]), a[12])) {
+    if (gb_latent_attention_tc_launch(op_ptr<const float>(a[0]), op_ptr<const bf16>(a[1]), op_ptr<const int>(a[3]), (int)a[4],
+                                      (int)a[5], (int)a[6], op_ptr<const int>(a[7]), op_ptr<const int>(a[8]),
+                                      op_ptr<const int>(a[22]), op_ptr<const float>(a[9]), a[10],
+                                      op_ptr<float>(a[11]), a[12], n, (int)a[21], H, r, (float)f[0],
+                                      op_ptr<const float>(a[20]), ctx->status, ctx->stream) == 0) {
+      GB_CHECK_LAUNCH("latent_attention (tensor cores)");
+      return 1;
+    }
+  }
   if (r > 512) GB_FAIL(GB_ERR_ARG, "latent_attention: latent size %d (at most 512)", r);
   const int Dk = r + dr;
   if (dr > 32 * LA_RR) GB_FAIL(GB_ERR_ARG, "latent_attention: rotated size %d (at most %d)", dr, 32 * LA_RR);

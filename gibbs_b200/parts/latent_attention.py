@@ -37,6 +37,9 @@ from .base import Mixer, PagedRows, TensorDecl, VECTOR, register_part
 from .runner import BranchPart, Runner, keep
 
 
+USE_TENSOR_CORES = True          # (the tests switch it off to compare the two kernels)
+
+
 def _workspace_rows() -> int:
     from ..ops.library import library
     return int(library(hybrid.LIBRARY).gb_latent_attention_workspace_rows())
@@ -119,7 +122,8 @@ class LatentAttention(BranchPart, Mixer):
                                    pages.shape[1], pages.shape[0], rn.tok_req, rn.tok_pos,
                                    fused.data_ptr() + 4 * self.gate_col if self.gated else 0, fused.stride(0),
                                    lat.data_ptr(), lat.stride(0), rn.N, H, r, dr, self.window or 0, rn.max_context,
-                                   ws.data_ptr(), keep(rn, self.sink)], [self.scale])
+                                   ws.data_ptr(), keep(rn, self.sink), rn.R if USE_TENSOR_CORES else 0,
+                                   rn.q_start if USE_TENSOR_CORES else 0], [self.scale])
         o = rn.buffer("la_heads_out", H * dv)
         rn.op("head_linear", [lat.data_ptr(), lat.stride(0), r, keep(rn, self.uv), ops.dtype_code(self.uv.dtype),
                               o.data_ptr(), ops.dtype_code(o.dtype), o.stride(0), dv, rn.N, H, dv, r],

@@ -345,6 +345,41 @@ def test_tensor_core_attention_against_the_generic_kernel(cfg, layer, monkeypatc
         assert rel_rows(outs[(True, rid)], outs[(False, rid)]).max() < 2e-2
 
 
+@pytest.mark.parametrize("heads,dim,vdim,kv_rank", [(4, 16, 16, 64), (3, 8, 20, 24), (5, 24, 8, 136), (16, 32, 32, 256),
+                                                    (6, 16, 24, 320), (8, 32, 16, 512), (64, 8, 8, 40), (1, 16, 16, 8)])
+def test_tensor_core_latent_attention_against_the_generic_kernel(heads, dim, vdim, kv_rank, monkeypatch):
+    """bfloat16: every width class of the kernel that takes steps with portions of prompts (latents of 8 to 512
+    entries, also no multiples of 64; 1 to 64 heads, also counts that do not divide a tile's 64 rows), against the
+    plain implementation and the generic kernel: whole, cut so that tiles end inside key tiles and pages, decoded
+    (which the generic kernel does either way), and a portion beside single tokens of another request."""
+    from gibbs_b200.parts import latent_attention
+    cfg = one_layer("latent_attention", lat(heads, dim, vdim, kv_rank, 0.3), 64)
+    W = make_weights(cfg, 15)
+    T = 330
+    h = bf(torch.randn(T, 64, generator=gen(16)))
+    want = plain_mixer(cfg, 0, W, h)
+    outs = {}
+    for tc in (True, False):
+        monkeypatch.setattr(latent_attention, "USE_TENSOR_CORES", tc)
+        part = part_of(cfg, 0, W, "bfloat16")
+        hz = PartHarness(part, n_pages=64, page_size=16)
+        for rid, cuts in (("whole", [T]), ("cut", [70, 9, 130, 1, 65, 55]), ("decoded", [T - 30, 1])):
+            outs[(tc, rid)] = hz.run_cut(rid, h, cuts)
+            check_rows(outs[(tc, rid)], want, "bfloat16", what=f"tensor cores {tc}, {rid}")
+            hz.close(rid)
+        # a portion of one request beside single tokens of another, in one step
+        first = hz.feed_many({"a": h[:200], "b": h[:100]})
+        second = hz.feed_many({"a": h[200:201], "b": h[100:T]})
+        third = hz.feed_many({"a": h[201:T]})
+        outs[(tc, "mixed a")] = torch.cat([first["a"], second["a"], third["a"]], 0)
+        outs[(tc, "mixed b")] = torch.cat([first["b"], second["b"]], 0)
+        check_rows(outs[(tc, "mixed a")], want, "bfloat16", what=f"tensor cores {tc}, mixed a")
+        check_rows(outs[(tc, "mixed b")], want, "bfloat16", what=f"tensor cores {tc}, mixed b")
+    assert not torch.equal(outs[(True, "whole")], outs[(False, "whole")])       # (two kernels did run)
+    for rid in ("whole", "cut", "mixed a", "mixed b"):
+        assert rel_rows(outs[(True, rid)], outs[(False, rid)]).max() < 2e-2
+
+
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(2, 1, 4, 4), (3, 3, 12, 20), (2, 2, 20, 72), (4, 2, 32, 8), (2, 1, 48, 36),
                                                      (4, 1, 64, 64), (1, 1, 100, 12), (2, 1, 128, 40), (1, 1, 160, 16),
                                                      (2, 2, 256, 24)])
