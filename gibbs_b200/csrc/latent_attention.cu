@@ -381,6 +381,9 @@ __global__ void latent_attention_merge_kernel(const float* ws, int splits, const
 
 }  // namespace
 
+bool gb_head_linear_tc_takes(int n, int I, long long ldx, long long xh, const void* x, const void* W);
+void gb_head_linear_tc_launch(const float* x, long long ldx, long long xh, const bf16* W, void* out, bool out_bf16,
+                              long long ldo, long long oh, int n, int H, int O, int I, cudaStream_t stream);
 bool gb_latent_attention_tc_takes(int n, int R, int H, int r, int dr, int window, bool pages_bf16, const void* pages,
                                   const void* qp, const void* out, long long ldo);
 int gb_latent_attention_tc_launch(const float* qp, const bf16* pages, const int* block_table, int bt_stride, int page_size,
@@ -435,10 +438,18 @@ GB_OP(gb_op_latent_prep) {
 }
 
 // a0 x (f32), a1 its row stride, a2 elements between heads in a row, a3 W [H, O, I], a4 its dtype, a5 out, a6 its
-// dtype, a7 its row stride, a8 elements between heads in a row, a9 rows, a10 heads, a11 O, a12 I
+// dtype, a7 its row stride, a8 elements between heads in a row, a9 rows, a10 heads, a11 O, a12 I; flags bit 0: the
+// generic kernels whatever the sizes
 GB_OP(gb_op_head_linear) {
   const int n = (int)a[9], H = (int)a[10], O = (int)a[11], I = (int)a[12];
   if (n <= 0) return 0;
+  if (a[4] == GB_BF16 && !(flags & 1) &&
+      gb_head_linear_tc_takes(n, I, a[1], a[2], op_ptr<const void>(a[0]), op_ptr<const void>(a[3]))) {
+    gb_head_linear_tc_launch(op_ptr<const float>(a[0]), a[1], a[2], op_ptr<const bf16>(a[3]), op_ptr<void>(a[5]),
+                             a[6] == GB_BF16, a[7], a[8], n, H, O, I, ctx->stream);
+    GB_CHECK_LAUNCH("head_linear (tensor cores)");
+    return 1;
+  }
   const bool small = n <= HL_SMALL_ROWS && (size_t)n * I * sizeof(float) <= 48 * 1024;
   const dim3 grid = small ? dim3(gb_div_up(O, 8), H) : dim3(gb_div_up(O, 64), gb_div_up(n, 64), H);
   const dim3 block(256);

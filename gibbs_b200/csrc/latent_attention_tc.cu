@@ -280,7 +280,108 @@ template <int RP> int ltc_launch(const LtcParams& p, int tiles, int R, cudaStrea
   return 0;
 }
 
+// out[t, h, :] = x[t, h, :] W[h]^T on tensor cores, for the two per-head products around the attention (W_uk^T on the
+// queries, W_uv on the weighted latents) when a step has rows enough.  A CTA takes 64 rows x 64 outputs of one head
+// in steps of 32 inputs; x is 32-bit and rounded to bfloat16 on its way into shared memory, as the framework's other
+// products round their inputs; the next step's operands are on their way in registers while this step's multiply.
+constexpr int HLT_STRIDE = 40;     // bfloat16 entries a row of a 64 x 32 tile takes (80 bytes: ldmatrix without conflicts)
+
+template <typename TO>
+__global__ void __launch_bounds__(128) head_linear_tc_kernel(const float* x, long long ldx, long long xh,
+                                                             const bf16* __restrict__ W, TO* out, long long ldo,
+                                                             long long oh, int n, int O, int I) {
+  __shared__ __align__(16) bf16 As[64 * HLT_STRIDE];
+  __shared__ __align__(16) bf16 Bs[64 * HLT_STRIDE];
+  pdl_trigger();
+  const int lane = threadIdx.x & 31, wm = threadIdx.x >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int h = blockIdx.z, r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+  const float* xb = x + (size_t)h * xh;
+  const bf16* wb = W + (size_t)h * O * I;
+  float acc[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  float4 ra[4];
+  uint4 rb[2];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int idx = threadIdx.x + 128 * u, row = idx >> 3, c = k0 + 4 * (idx & 7);
+      ra[u] = (r0 + row < n && c < I) ? *reinterpret_cast<const float4*>(xb + (size_t)(r0 + row) * ldx + c)
+                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int idx = threadIdx.x + 128 * u, row = idx >> 2, c = k0 + 8 * (idx & 3);
+      rb[u] = (c0 + row < O && c < I) ? *reinterpret_cast<const uint4*>(wb + (size_t)(c0 + row) * I + c)
+                                      : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  auto put = [&]() {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int idx = threadIdx.x + 128 * u, row = idx >> 3, c = 4 * (idx & 7);
+      uint2 w;
+      w.x = ltc_pack(ra[u].x, ra[u].y);
+      w.y = ltc_pack(ra[u].z, ra[u].w);
+      *reinterpret_cast<uint2*>(As + row * HLT_STRIDE + c) = w;
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int idx = threadIdx.x + 128 * u, row = idx >> 2, c = 8 * (idx & 3);
+      *reinterpret_cast<uint4*>(Bs + row * HLT_STRIDE + c) = rb[u];
+    }
+  };
+  pdl_wait();
+  fetch(0);
+  for (int k0 = 0; k0 < I; k0 += 32) {
+    __syncthreads();                                       // the last step's tiles have been used
+    put();
+    __syncthreads();
+    if (k0 + 32 < I) fetch(k0 + 32);
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      unsigned a[4];
+      ltc_ldmatrix(a, As + (wm * 16 + (lane & 15)) * HLT_STRIDE + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        unsigned bb[4];
+        ltc_ldmatrix(bb, Bs + (np * 16 + (lane & 7) + (lane >> 4) * 8) * HLT_STRIDE + ks * 16 + ((lane >> 3) & 1) * 8);
+        ltc_mma(acc[2 * np], a, bb[0], bb[1]);
+        ltc_mma(acc[2 * np + 1], a, bb[2], bb[3]);
+      }
+    }
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int row = r0 + wm * 16 + g + 8 * half;
+    if (row >= n) continue;
+    TO* dst = out + (size_t)row * ldo + (size_t)h * oh;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int col = c0 + 8 * j + 2 * t4;
+      if (col < O) dst[col] = from_f32<TO>(acc[j][2 * half]);
+      if (col + 1 < O) dst[col + 1] = from_f32<TO>(acc[j][2 * half + 1]);
+    }
+  }
+}
+
 }  // namespace
+
+// Whether the per-head product runs on tensor cores: bfloat16 weights whose rows can be read in 16-byte pieces, 32-bit
+// inputs readable four at a time, and at least a tile of rows.
+bool gb_head_linear_tc_takes(int n, int I, long long ldx, long long xh, const void* x, const void* W) {
+  return n >= 64 && I % 8 == 0 && ldx % 4 == 0 && xh % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)W & 15) == 0;
+}
+
+void gb_head_linear_tc_launch(const float* x, long long ldx, long long xh, const bf16* W, void* out, bool out_bf16,
+                              long long ldo, long long oh, int n, int H, int O, int I, cudaStream_t stream) {
+  const dim3 grid(gb_div_up(O, 64), gb_div_up(n, 64), H), block(128);
+  if (out_bf16)
+    gb_launch(head_linear_tc_kernel<bf16>, grid, block, 0, stream, x, ldx, xh, W, static_cast<bf16*>(out), ldo, oh, n, O, I);
+  else
+    gb_launch(head_linear_tc_kernel<float>, grid, block, 0, stream, x, ldx, xh, W, static_cast<float*>(out), ldo, oh, n, O, I);
+}
 
 // Whether the tensor-core kernel takes a launch: bfloat16 pages whose rows can be copied in 16-byte pieces, no rotated
 // part, no window, at most 64 heads, and a step that carries portions (eight tokens a request on average).

@@ -115,7 +115,7 @@ class LatentAttention(BranchPart, Mixer):
                               dn, dr, r, qp.data_ptr()], [self.eps])
         rn.op("head_linear", [fused.data_ptr(), fused.stride(0), dn + dr, keep(rn, self.uk_t),
                               ops.dtype_code(self.uk_t.dtype), qp.data_ptr(), ops.F32, qp.stride(0), Dk, rn.N, H, r, dn],
-              label="head_linear:absorb")
+              label="head_linear:absorb", flags=0 if USE_TENSOR_CORES else 1)
         lat = rn.buffer("la_latent_out", H * r, torch.float32)
         ws = rn.buffer("la_partial", r + 2, torch.float32, fixed_rows=_workspace_rows())
         rn.op("latent_attention", [qp.data_ptr(), pages.data_ptr(), ops.dtype_code(pages.dtype), table, bt_stride,
@@ -127,7 +127,7 @@ class LatentAttention(BranchPart, Mixer):
         o = rn.buffer("la_heads_out", H * dv)
         rn.op("head_linear", [lat.data_ptr(), lat.stride(0), r, keep(rn, self.uv), ops.dtype_code(self.uv.dtype),
                               o.data_ptr(), ops.dtype_code(o.dtype), o.stride(0), dv, rn.N, H, dv, r],
-              label="head_linear:values")
+              label="head_linear:values", flags=0 if USE_TENSOR_CORES else 1)
         (rn.add_linear if accumulate else rn.linear)(o, self.o, None, out, role="latent_out")
 
 

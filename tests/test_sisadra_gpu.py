@@ -376,8 +376,9 @@ def test_tensor_core_latent_attention_against_the_generic_kernel(heads, dim, vdi
         check_rows(outs[(tc, "mixed a")], want, "bfloat16", what=f"tensor cores {tc}, mixed a")
         check_rows(outs[(tc, "mixed b")], want, "bfloat16", what=f"tensor cores {tc}, mixed b")
     assert not torch.equal(outs[(True, "whole")], outs[(False, "whole")])       # (two kernels did run)
+    # (the tensor-core path also rounds the inputs of the two per-head products to bfloat16, as products do)
     for rid in ("whole", "cut", "mixed a", "mixed b"):
-        assert rel_rows(outs[(True, rid)], outs[(False, rid)]).max() < 2e-2
+        assert rel_rows(outs[(True, rid)], outs[(False, rid)]).max() < 4e-2
 
 
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(2, 1, 4, 4), (3, 3, 12, 20), (2, 2, 20, 72), (4, 2, 32, 8), (2, 1, 48, 36),
