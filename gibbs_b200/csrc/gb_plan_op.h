@@ -13,7 +13,10 @@
 // address), its 3 floating-point operands and its flags.  It launches its kernels on
 // ctx->stream and returns how many it launched, or a negative number to fail the step.
 // Before the call the 32-bit residual stream is whole (sums that a product had left to be added
-// are added).
+// are added), unless the record's flags have GB_OP_TAKES_PENDING: then the function gets those sums
+// (ctx->pend ...) and must itself leave the stream whole: x[m, :] += pend[0][m, :] + pend[1][m, :] + ...
+// (+ pend_bias), in this order, for every row of the step.  Steps of fewer than GB_OP_PENDING_MIN_ROWS tokens are
+// made whole before the call whatever the flags.
 #pragma once
 #include <cuda_runtime.h>
 
@@ -22,7 +25,16 @@ struct GbPlanCtx {
   int* status;               // the device's status word (a kernel sets it nonzero to report a failure)
   const long long* sym;      // the step's symbols, indexed by GbPlanSymbol
   int n_sym;
+  // for a record whose flags have GB_OP_TAKES_PENDING (null / 0 otherwise, and when nothing is pending)
+  float* residual;           // the 32-bit stream [tokens, residual_ld]
+  long long residual_ld;
+  const float* pend;         // [pend_splits][tokens * residual_ld] sums a product left to be added
+  int pend_splits;
+  const float* pend_bias;    // [residual_ld] or null
 };
+
+#define GB_OP_TAKES_PENDING (1 << 30)
+#define GB_OP_PENDING_MIN_ROWS 64
 
 typedef int (*GbPlanOpFn)(const GbPlanCtx* ctx, const long long* a, const double* f, int flags);
 

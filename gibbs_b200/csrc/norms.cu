@@ -92,13 +92,30 @@ __global__ void row_norm_kernel(const float* x, long long ldx, const float* __re
   }
 }
 
+// x[m, :] += pend[0][m, :] + pend[1][m, :] + ... (+ bias), in this order: what a product left to be added into the
+// stream, for a launch that cannot add it while it reads its rows.
+__global__ void norm_pending_add_kernel(float* __restrict__ x, long long ldx, const float* pend, int splits,
+                                        const float* __restrict__ bias, long long n_rows, int dim) {
+  pdl_trigger();
+  pdl_wait();
+  const long long total = n_rows * dim;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long m = i / dim;
+    const int d = (int)(i - m * dim);
+    float v = x[(size_t)m * ldx + d];
+    for (int u = 0; u < splits; ++u) v += pend[(size_t)u * total + i];
+    if (bias) v += bias[d];
+    x[(size_t)m * ldx + d] = v;
+  }
+}
+
 // One warp a row, the row in registers as V4 pieces of four values a lane (dim <= 128 * V4, a multiple of 4, rows
 // 16-byte aligned): no block-wide sums, 16-byte loads and packed stores.  Which kernel runs depends on the row's
 // length and alignment only, never on the number of rows.
-template <typename TO, int V4>
+template <typename TO, int V4, bool PEND>
 __global__ void __launch_bounds__(128)
 row_norm_warp_kernel(const float* x, long long ldx, const float* __restrict__ gain, TO* out, const int* rows, int n, int dim,
-                     int kind, float eps) {
+                     int kind, float eps, const float* pend, int pend_splits, const float* __restrict__ pend_bias) {
   pdl_trigger();
   const int lane = threadIdx.x & 31;
   const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -112,6 +129,19 @@ row_norm_warp_kernel(const float* x, long long ldx, const float* __restrict__ ga
   for (int i = 0; i < V4; ++i) {
     const int d = 4 * (lane + 32 * i);
     v[i] = d < dim ? *reinterpret_cast<const float4*>(row + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (PEND && d < dim) {                                 // (an instantiation of its own: the stores order the loads)
+      // sums a product left to be added into the stream: added here in their order, and the row is made whole
+      const size_t total = (size_t)n * dim, at = (size_t)src * dim + d;
+      for (int u = 0; u < pend_splits; ++u) {
+        const float4 q = *reinterpret_cast<const float4*>(pend + u * total + at);
+        v[i].x += q.x; v[i].y += q.y; v[i].z += q.z; v[i].w += q.w;
+      }
+      if (pend_bias != nullptr) {
+        const float4 q = *reinterpret_cast<const float4*>(pend_bias + d);
+        v[i].x += q.x; v[i].y += q.y; v[i].z += q.z; v[i].w += q.w;
+      }
+      *reinterpret_cast<float4*>(const_cast<float*>(row) + d) = v[i];
+    }
     s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
   }
   const float mean = kind == NORM_LAYER ? warp_sum(s) / (float)dim : 0.f;
@@ -348,11 +378,38 @@ GB_OP(gb_op_row_norm) {
   if (n <= 0) return 0;
   if (kind != NORM_LAYER && kind != NORM_RMS) GB_FAIL(GB_ERR_ARG, "row_norm: kind %d", kind);
   const size_t out_bytes = a[4] == GB_BF16 ? 2 : 4;
-  if (dim % 4 == 0 && dim <= 2048 && a[1] % 4 == 0 && (a[0] & 15) == 0 && (a[2] & 15) == 0 && (a[3] & (4 * out_bytes - 1)) == 0) {
+  const bool by_warps = dim % 4 == 0 && dim <= 2048 && a[1] % 4 == 0 && (a[0] & 15) == 0 && (a[2] & 15) == 0 &&
+                        (a[3] & (4 * out_bytes - 1)) == 0;
+  // sums a product left to be added into the stream (a record with GB_OP_TAKES_PENDING): the kernel with a warp a row
+  // adds them while it reads its rows, when these are all of the stream's rows; else they are added first
+  const float* pend = (flags & GB_OP_TAKES_PENDING) && ctx->pend_splits > 0 ? ctx->pend : nullptr;
+  int launched = 0;
+  if (pend != nullptr) {
+    const long long N = ctx->sym != nullptr ? ctx->sym[GB_SYM_TOKENS] : n;
+    const bool folds = by_warps && a[5] == 0 && op_ptr<float>(a[0]) == ctx->residual && a[1] == ctx->residual_ld &&
+                       dim == ctx->residual_ld && n == N && ((uintptr_t)pend & 15) == 0 &&
+                       (ctx->pend_bias == nullptr || ((uintptr_t)ctx->pend_bias & 15) == 0);
+    if (!folds) {
+      const long long total = N * ctx->residual_ld;
+      const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+      gb_launch(norm_pending_add_kernel, dim3(blocks), dim3(256), 0, ctx->stream, ctx->residual, ctx->residual_ld, pend,
+                ctx->pend_splits, ctx->pend_bias, N, (int)ctx->residual_ld);
+      GB_CHECK_LAUNCH("row_norm (pending sums)");
+      pend = nullptr;
+      launched = 1;
+    }
+  }
+  if (by_warps) {
     const dim3 wgrid(gb_div_up(n, 4)), wblock(128);
 #define WARP_NORM(TO, V4)                                                                                               \
-    gb_launch(row_norm_warp_kernel<TO, V4>, wgrid, wblock, 0, ctx->stream, op_ptr<const float>(a[0]), a[1],              \
-              op_ptr<const float>(a[2]), op_ptr<TO>(a[3]), op_ptr<const int>(a[5]), n, dim, kind, (float)f[0])
+    if (pend != nullptr)                                                                                                \
+      gb_launch(row_norm_warp_kernel<TO, V4, true>, wgrid, wblock, 0, ctx->stream, op_ptr<const float>(a[0]), a[1],      \
+                op_ptr<const float>(a[2]), op_ptr<TO>(a[3]), op_ptr<const int>(a[5]), n, dim, kind, (float)f[0], pend,    \
+                ctx->pend_splits, ctx->pend_bias);                                                                       \
+    else                                                                                                                \
+    gb_launch(row_norm_warp_kernel<TO, V4, false>, wgrid, wblock, 0, ctx->stream, op_ptr<const float>(a[0]), a[1],       \
+              op_ptr<const float>(a[2]), op_ptr<TO>(a[3]), op_ptr<const int>(a[5]), n, dim, kind, (float)f[0], pend,          \
+              pend != nullptr ? ctx->pend_splits : 0, pend != nullptr ? ctx->pend_bias : nullptr)
 #define WARP_NORM_V4(TO)                                                                                                \
     do {                                                                                                                \
       if (dim <= 128) WARP_NORM(TO, 1); else if (dim <= 256) WARP_NORM(TO, 2); else if (dim <= 512) WARP_NORM(TO, 4);   \
@@ -362,7 +419,7 @@ GB_OP(gb_op_row_norm) {
 #undef WARP_NORM_V4
 #undef WARP_NORM
     GB_CHECK_LAUNCH("row_norm (a warp a row)");
-    return 1;
+    return launched + 1;
   }
   const dim3 grid(n), block(norm_threads(dim));
   if (a[4] == GB_BF16)
@@ -372,7 +429,7 @@ GB_OP(gb_op_row_norm) {
     gb_launch(row_norm_kernel<float>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], op_ptr<const float>(a[2]),
               op_ptr<float>(a[3]), op_ptr<const int>(a[5]), dim, kind, (float)f[0]);
   GB_CHECK_LAUNCH("row_norm");
-  return 1;
+  return launched + 1;
 }
 
 // a0 x (f32, the stream), a1 its row stride, a2 y (f32), a3 its row stride, a4 gain, a5 rows, a6 dim, a7 kind,

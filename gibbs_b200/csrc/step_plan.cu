@@ -383,7 +383,9 @@ int run_registered(Walk& w, const PlanOp& o) {
   }
   // such an operation sees the stream whole: what a product left to be added is added first, and
   // what this file remembers about the stream no longer holds afterwards
-  if (w.pend_splits > 0) {
+  // (it adds them itself; the few rows of a small step, each with many partial sums, are added faster here)
+  const bool takes = (o.flags & GB_OP_TAKES_PENDING) != 0 && w.pend_splits > 0 && w.sym[S_N] >= GB_OP_PENDING_MIN_ROWS;
+  if (w.pend_splits > 0 && !takes) {
     const int N = (int)w.sym[S_N];
     PLAN_CALL(w, F_ADD_PENDING, ((AddPendingFn)g_fn[F_ADD_PENDING])(
         w.residual, w.residual_ld, w.ws, w.pend_splits, w.pend_bias, (long long)N, (int)w.residual_ld, w.stream));
@@ -399,6 +401,12 @@ int run_registered(Walk& w, const PlanOp& o) {
   ctx.status = w.status;
   ctx.sym = w.sym;
   ctx.n_sym = S_COUNT;
+  ctx.residual = takes ? w.residual : nullptr;
+  ctx.residual_ld = w.residual_ld;
+  ctx.pend = takes ? w.ws : nullptr;
+  ctx.pend_splits = takes ? w.pend_splits : 0;
+  ctx.pend_bias = takes ? w.pend_bias : nullptr;
+  w.pend_splits = 0;
   const int rc = g_registered[i].fn(&ctx, a, o.f, o.flags);
   if (rc < 0) {
     snprintf(gb_error_buffer(), 512, "gb_plan_run: the registered operation '%s' failed with code %d",

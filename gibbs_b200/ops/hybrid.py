@@ -26,11 +26,13 @@ OPERATIONS = ("row_norm", "norm_add", "clamped_glu", "gelu_mul_rows", "gated_gro
               "delta_scan")
 
 NORM_LAYER, NORM_RMS = 0, 1
+TAKES_PENDING = 1 << 30          # a record's flag: the operation adds the sums a product left pending itself
 
 
 class _Ctx(ctypes.Structure):
     _fields_ = [("stream", ctypes.c_void_p), ("status", ctypes.c_void_p), ("sym", ctypes.c_void_p),
-                ("n_sym", ctypes.c_int)]
+                ("n_sym", ctypes.c_int), ("residual", ctypes.c_void_p), ("residual_ld", ctypes.c_longlong),
+                ("pend", ctypes.c_void_p), ("pend_splits", ctypes.c_int), ("pend_bias", ctypes.c_void_p)]
 
 
 _FN: dict = {}
@@ -58,7 +60,8 @@ def call(name: str, a, f=(), flags: int = 0, device=None) -> int:
     fa = (ctypes.c_double * 3)(*[float(v) for v in f])
     status = device_status(device if device is not None else torch.device("cuda", torch.cuda.current_device()))
     stream = _stream()
-    ctx = _Ctx(stream.value if isinstance(stream, ctypes.c_void_p) else stream, status.data_ptr(), None, 0)
+    ctx = _Ctx(stream.value if isinstance(stream, ctypes.c_void_p) else stream, status.data_ptr(), None, 0, None, 0, None, 0,
+               None)                # (called directly, nothing is ever pending)
     rc = fn(ctypes.byref(ctx), ia, fa, ctypes.c_int(flags))
     if rc < 0:
         check(library(LIBRARY), rc)

@@ -75,7 +75,7 @@ class RowNorm(Norm):
         out = rn.buffer("normed_wanted" if wanted_rows else "normed", self.dim)
         rn.op("row_norm", [x.data_ptr(), x.stride(0), keep(rn, self.gain), out.data_ptr(), ops.dtype_code(out.dtype),
                            rn.want_rows if wanted_rows else 0, rn.W if wanted_rows else rn.N, self.dim, self.KIND],
-              [self.eps], label="row_norm")
+              [self.eps], label="row_norm", flags=hybrid.TAKES_PENDING)
         return out
 
     def add_normed(self, rn: Runner, x: torch.Tensor, y: torch.Tensor, copy: torch.Tensor = None, then=None):
