@@ -4,7 +4,8 @@ Two kinds of memory, both sized once at start:
 
 * **Pages** for mixers that keep keys and values per position.  Entries of the
   model's order with the same retention rule form a *group* (all keys; the
-  last ``window`` keys; the keys of the current block of ``block`` positions).  A group has a pool of page ids of its own and every
+  last ``window`` keys, with or without the sequence's first ``keep_first`` ones; the keys of the current block of
+  ``block`` positions).  A group has a pool of page ids of its own and every
   request has one block table per group; a page id addresses the same page in
   the key and value tensors of every entry of the group
   (``[n_pages, kv_heads, page_size, head_dim]`` each), and in the row tensors
@@ -50,6 +51,7 @@ class PagedKVView:
     writable: bool
     window: Optional[int]
     block: Optional[int] = None        # the pages keep the current block of this many positions
+    keep_first: int = 0                # beside a window: the first positions of a sequence stay as well
 
 
 @dataclass
@@ -74,6 +76,7 @@ class _Group:
     window: Optional[int]
     pool: IdPool
     block: Optional[int] = None                     # positions seen in blocks of this many instead of a window
+    keep_first: int = 0                             # beside a window: the first positions stay
     entries: list = field(default_factory=list)     # (entry index, need index)
 
 
@@ -124,7 +127,8 @@ class CacheManager:
                         count = n_pages[rule] if isinstance(n_pages, dict) else n_pages
                         by_window[rule] = len(self.groups)
                         self.groups.append(_Group(need.window, IdPool(count, "page"),
-                                                  block=getattr(need, "block", None)))
+                                                  block=getattr(need, "block", None),
+                                                  keep_first=int(getattr(need, "keep_first", 0) or 0)))
                     g = by_window[rule]
                     self.groups[g].entries.append((e, k))
                     self._group_of[(e, k)] = g
@@ -217,6 +221,13 @@ class CacheManager:
             return 0
         return max(0, start_pos - group.window + 1) // self.page_size
 
+    def _passed_pages(self, group: _Group, start_pos: int, table: list) -> range:
+        """Indices (in the block table) of the pages no step from start_pos on reads: those in front of
+        the first needed one, but not the pages that hold a sequence's kept first positions."""
+        first = min(self._first_needed_page(group, start_pos), len(table))
+        kept = self.pages_needed(group.keep_first) if group.keep_first else 0
+        return range(min(kept, first), first)
+
     def pages_wanted(self, wants) -> list[int]:
         """Pages each group's pool must still give for ``wants``, a list of
         (request cache, new length), once every request of the list has given
@@ -225,8 +236,7 @@ class CacheManager:
         for rc, new_length in wants:
             for g, group in enumerate(self.groups):
                 table = rc.block_tables[g]
-                first = self._first_needed_page(group, rc.length)
-                freed = sum(1 for p in table[:first] if p >= 0)
+                freed = sum(1 for i in self._passed_pages(group, rc.length, table) if table[i] >= 0)
                 need[g] += max(self.pages_needed(new_length) - len(table), 0) - freed
         return need
 
@@ -253,8 +263,7 @@ class CacheManager:
         for rc, _ in wants:
             for g, group in enumerate(self.groups):
                 table = rc.block_tables[g]
-                first = self._first_needed_page(group, rc.length)
-                for i in range(min(first, len(table))):
+                for i in self._passed_pages(group, rc.length, table):
                     if table[i] >= 0:
                         group.pool.give_back(table[i])
                         table[i] = -1
@@ -344,7 +353,8 @@ class CacheManager:
                 elif isinstance(need, PagedKV):
                     kp, vp = self._pages[(owner, k)]
                     g = self._group_of[(owner, k)]
-                    views.append(PagedKVView(kp, vp, block_tables[g], self.page_size, reads is None, need.window, need.block))
+                    views.append(PagedKVView(kp, vp, block_tables[g], self.page_size, reads is None, need.window, need.block,
+                                             int(getattr(need, "keep_first", 0) or 0)))
                 else:
                     views.append(SlotView(self._slot_views[(owner, k)], slot_ids, host_slot_ids))
             out.append(views)

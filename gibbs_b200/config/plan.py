@@ -84,6 +84,9 @@ class ModelPlan:
     # checkpoint tensors that may be present although no part reads them (a layer without a
     # feed-forward whose checkpoint still carries that sublayer's norms, say): fnmatch patterns
     ignorable: tuple[str, ...] = ()
+    # for random weights: (fnmatch pattern of checkpoint names, value) pairs for vectors that are neither noise nor
+    # gains around one (a norm weight stored around zero, a scale per channel); the first match wins
+    random_values: tuple[tuple[str, float], ...] = ()
 
     def validate(self) -> None:
         for i, e in enumerate(self.order):

@@ -8,9 +8,11 @@
 //                        every head in adjacent pairs (2i, 2i+1) by pos * inv_freq[i] (angle in 32-bit)
 //  gb_op_sink_attention  out[t, h, :] = gate * sum_j p_j v_j over the visible keys j (0 <= pos - j < window, or
 //                        all j <= pos), s_j = cap(scale * q . k_j), cap(s) = c * tanh(s / c) when c > 0,
-//                        p_j = exp(s_j) / (sink + sum_i exp(s_i)) with sink = 1 when the softmax has a sink (a key
-//                        of score 0 without a value) and 0 otherwise, gate = sigmoid(gate logit) per output
-//                        element, or 1.  Scores, weights and sums are 32-bit.
+//                        p_j = exp(s_j) / (sink + sum_i exp(s_i)) with sink = exp(z) when the softmax has a sink (a key
+//                        of score z without a value: 0, or a learned number per head that is neither scaled nor
+//                        capped) and 0 otherwise, gate = sigmoid(gate logit) per output element, or 1.  With
+//                        `keep_first` > 0 a windowed position also sees the first `keep_first` positions of its
+//                        sequence.  Scores, weights and sums are 32-bit.
 //
 // Pages: keys [n_pages, kv_heads, page_size, dim], values [n_pages, kv_heads, page_size, vdim].  A page id
 // outside the pool is never dereferenced: the access is skipped and *status is set.
@@ -63,7 +65,8 @@ __global__ void embed_scaled_kernel(const T* __restrict__ table, const int* ids,
 }
 
 // How q and k are normed and turned (qk_prep's flags).
-enum { PREP_NORM_WHOLE = 1, PREP_Q_BF16 = 2, PREP_PAGES_BF16 = 4, PREP_NORM_HEAD = 8, PREP_ROT_HALVES = 16 };
+enum { PREP_NORM_WHOLE = 1, PREP_Q_BF16 = 2, PREP_PAGES_BF16 = 4, PREP_NORM_HEAD = 8, PREP_ROT_HALVES = 16,
+       PREP_NORM_AFTER = 32 };
 
 // One normed and rotated element of a projection: entry d of a head of `dim` entries that starts at `base`.
 // `gain` is indexed like the projection (norm over the whole projection) or by d (`gain_per_head`: one gain
@@ -102,6 +105,8 @@ __global__ void qk_prep_kernel(const float* fused, long long ld, int k_col, int 
   const int pos = tok_pos[t];
   const bool writes = k_pages != nullptr;
   const bool whole = mode & PREP_NORM_WHOLE, per_head = mode & PREP_NORM_HEAD, halves = mode & PREP_ROT_HALVES;
+  // PREP_NORM_AFTER: every head is turned first and then divided by the root mean square of the TURNED head (no gain)
+  const bool after = mode & PREP_NORM_AFTER;
   int page = -1;
   if (writes) page = block_table[(size_t)tok_req[t] * bt_stride + pos / page_size];
   pdl_wait();
@@ -126,9 +131,18 @@ __global__ void qk_prep_kernel(const float* fused, long long ld, int k_col, int 
       for (int d = lane; d < dim; d += 32) ss += row[h * dim + d] * row[h * dim + d];
       rstd = 1.0f / sqrtf(warp_sum(ss) / (float)dim + eps);
     }
+    float post = 1.f;
+    if (after) {
+      float ss = 0.f;
+      for (int d = lane; d < dim; d += 32) {
+        const float v = prep_element(row, nullptr, true, 1.f, h * dim, d, rot_dims, halves, inv_freq, pos);
+        ss += v * v;
+      }
+      post = 1.0f / sqrtf(warp_sum(ss) / (float)dim + eps);
+    }
     for (int d = lane; d < dim; d += 32)
-      q_out[(size_t)t * ldq + h * dim + d] = from_f32<TQ>(prep_element(row, normed ? q_gain : nullptr, per_head, rstd,
-                                                                       h * dim, d, rot_dims, halves, inv_freq, pos));
+      q_out[(size_t)t * ldq + h * dim + d] = from_f32<TQ>(post * prep_element(row, normed ? q_gain : nullptr, per_head, rstd,
+                                                                              h * dim, d, rot_dims, halves, inv_freq, pos));
   }
   if (!writes) return;
   if (page < 0 || page >= n_pages) {
@@ -145,9 +159,18 @@ __global__ void qk_prep_kernel(const float* fused, long long ld, int k_col, int 
       rstd = 1.0f / sqrtf(warp_sum(ss) / (float)dim + eps);
     }
     TC* dst = k_pages + (((size_t)page * G + g) * page_size + slot) * ((size_t)maps * dim) + (size_t)m * dim;
+    float post = 1.f;
+    if (after) {
+      float ss = 0.f;
+      for (int d = lane; d < dim; d += 32) {
+        const float v = prep_element(row + k_col, nullptr, true, 1.f, h * dim, d, rot_dims, halves, inv_freq, pos);
+        ss += v * v;
+      }
+      post = 1.0f / sqrtf(warp_sum(ss) / (float)dim + eps);
+    }
     for (int d = lane; d < dim; d += 32)
-      dst[d] = from_f32<TC>(prep_element(row + k_col, normed ? k_gain : nullptr, per_head, rstd, h * dim, d, rot_dims,
-                                         halves, inv_freq, pos));
+      dst[d] = from_f32<TC>(post * prep_element(row + k_col, normed ? k_gain : nullptr, per_head, rstd, h * dim, d, rot_dims,
+                                                halves, inv_freq, pos));
   }
   for (int i = threadIdx.x; i < G * vdim; i += blockDim.x) {
     const int g = i / vdim, d = i - g * vdim;
@@ -164,10 +187,12 @@ __global__ void qk_prep_kernel(const float* fused, long long ld, int k_col, int 
 // chunks are empty give the same bits.
 constexpr int SA_WARPS = 8, SA_KT = 32;
 
-// The sums over chunks s of exp(m_s - M) * (l_s, acc_s) with M = max(m_s, the sink's 0): what both the
+// The sums over chunks s of exp(m_s - M) * (l_s, acc_s) with M = max(m_s, the sink's score): what both the
 // attention kernel (one chunk) and the merge kernel (several) divide by and multiply with.
-__device__ __forceinline__ float sa_top(float m, int sink) { return sink ? fmaxf(m, 0.f) : m; }
-__device__ __forceinline__ float sa_sink_weight(float M, int sink) { return sink ? expf(0.f - M) : 0.f; }
+// (z: the sink's score, 0 unless the heads have learned ones)
+__device__ __forceinline__ float sa_sink_score(const float* __restrict__ scores, int head) { return scores ? scores[head] : 0.f; }
+__device__ __forceinline__ float sa_top(float m, int sink, float z) { return sink ? fmaxf(m, z) : m; }
+__device__ __forceinline__ float sa_sink_weight(float M, int sink, float z) { return sink ? expf(z - M) : 0.f; }
 
 template <typename TC, typename TQ, typename TO, int VR>
 __global__ void __launch_bounds__(32 * SA_WARPS)
@@ -175,7 +200,7 @@ sink_attention_kernel(const TQ* q, long long ldq, const TC* k_pages, const TC* v
                       int bt_stride, int page_size, int n_pages, const int* tok_req, const int* tok_pos,
                       const float* gate, long long ld_gate, TO* out, long long ldo, int H, int G, int dim, int vdim,
                       float scale, float softcap, int window, int sink, int splits, int chunk, float* ws, int maps,
-                      int blocked, int* status) {
+                      int blocked, const float* __restrict__ sink_scores, int keep_first, int* status) {
   // (H counts heads of `dim` entries: `maps` of them make one query head, and a key row holds `maps` keys side
   // by side, of which head h scores against number h % maps)
   extern __shared__ __align__(16) float sm[];
@@ -198,8 +223,13 @@ sink_attention_kernel(const TQ* q, long long ldq, const TC* k_pages, const TC* v
   const int* table = block_table + (size_t)tok_req[t] * bt_stride;
   // visible: the last `window` positions, or (`blocked`) the positions of pos's own block of `window`
   const int lo = window > 0 ? (blocked ? (pos / window) * window : max(0, pos - window + 1)) : 0;
-  const int k_begin = splits > 1 ? lo + (int)blockIdx.z * chunk : lo;
-  const int k_end = splits > 1 ? min(pos, k_begin + chunk - 1) : pos;
+  // the visible keys in order: the first `kept` positions of the sequence that lie in front of the window, then
+  // lo .. pos; key number v of this list is position v (v < kept) or lo + v - kept
+  const int kept = window > 0 ? min(keep_first, lo) : 0;
+  const int shift = lo - kept;
+  const int k_last = kept + pos - lo;
+  const int k_begin = splits > 1 ? (int)blockIdx.z * chunk : 0;
+  const int k_end = splits > 1 ? min(k_last, k_begin + chunk - 1) : k_last;
   pdl_wait();
   for (int i = threadIdx.x; i < warps * dim; i += blockDim.x) {
     const int w = i / dim, d = i - w * dim;
@@ -213,9 +243,10 @@ sink_attention_kernel(const TQ* q, long long ldq, const TC* k_pages, const TC* v
   for (int k0 = k_begin; k0 <= k_end; k0 += SA_KT) {
     __syncthreads();                                          // the last tile has been used (and qs is written)
     if (threadIdx.x < SA_KT) {
-      const int kp = k0 + threadIdx.x;
+      const int kv = k0 + threadIdx.x;
+      const int kp = kv < kept ? kv : kv + shift;
       long long at = -1;
-      if (kp <= k_end) {
+      if (kv <= k_end) {
         const int page = table[kp / page_size];
         if (page < 0 || page >= n_pages) atomicExch(status, STATUS_BAD_PAGE_READ);
         else at = ((long long)page * G + g) * page_size + kp % page_size;
@@ -274,9 +305,10 @@ sink_attention_kernel(const TQ* q, long long ldq, const TC* k_pages, const TC* v
     }
     return;
   }
-  const float M = sa_top(m, sink);
+  const float z = sa_sink_score(sink_scores, h / maps);
+  const float M = sa_top(m, sink, z);
   const float e = expf(m - M);
-  const float inv = 1.0f / fmaf(e, l, sa_sink_weight(M, sink));
+  const float inv = 1.0f / fmaf(e, l, sa_sink_weight(M, sink, z));
 #pragma unroll
   for (int i = 0; i < VR; ++i) {
     const int dv = lane + 32 * i;
@@ -291,7 +323,8 @@ sink_attention_kernel(const TQ* q, long long ldq, const TC* k_pages, const TC* v
 // chunk order; the sink joins as a chunk of maximum 0, weight 1 and no values.
 template <typename TO>
 __global__ void sink_attention_merge_kernel(const float* ws, int splits, const float* gate, long long ld_gate, TO* out,
-                                            long long ldo, int n, int H, int vdim, int sink) {
+                                            long long ldo, int n, int H, int vdim, int sink,
+                                            const float* __restrict__ sink_scores, int maps) {
   pdl_trigger();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -301,8 +334,9 @@ __global__ void sink_attention_merge_kernel(const float* ws, int splits, const f
   const float* w = ws + (size_t)idx * splits * (vdim + 2);
   float M = -INFINITY;
   for (int s = 0; s < splits; ++s) M = fmaxf(M, w[(size_t)s * (vdim + 2)]);
-  M = sa_top(M, sink);
-  float L = sa_sink_weight(M, sink);
+  const float z = sa_sink_score(sink_scores, h / maps);
+  M = sa_top(M, sink, z);
+  float L = sa_sink_weight(M, sink, z);
   for (int s = 0; s < splits; ++s) {
     const float ms = w[(size_t)s * (vdim + 2)];
     if (ms > -INFINITY) L = fmaf(expf(ms - M), w[(size_t)s * (vdim + 2) + 1], L);
@@ -328,14 +362,15 @@ GB_API int gb_sink_attention_workspace_rows() { return SA_WS_ROWS; }
 
 // The merge of chunks, for this file's kernel and for the tensor-core one (gated_attention_tc.cu).
 int gb_sink_attention_merge(const float* ws, int splits, const float* gate, long long ld_gate, void* out, int out_bf16,
-                            long long ldo, int n, int H, int vdim, int sink, cudaStream_t stream) {
+                            long long ldo, int n, int H, int vdim, int sink, const float* sink_scores, int maps,
+                            cudaStream_t stream) {
   const dim3 mgrid(gb_div_up((long long)n * H, 4));
   if (out_bf16)
     gb_launch(sink_attention_merge_kernel<bf16>, mgrid, dim3(128), 0, stream, ws, splits, gate, ld_gate, (bf16*)out, ldo, n,
-              H, vdim, sink);
+              H, vdim, sink, sink_scores, maps);
   else
     gb_launch(sink_attention_merge_kernel<float>, mgrid, dim3(128), 0, stream, ws, splits, gate, ld_gate, (float*)out, ldo,
-              n, H, vdim, sink);
+              n, H, vdim, sink, sink_scores, maps);
   GB_CHECK_LAUNCH("sink_attention_merge");
   return 1;
 }
@@ -344,6 +379,7 @@ int gb_sink_attention_merge(const float* ws, int splits, const float* gate, long
 // tokens (decoding) get many chunks, so that the GPU is occupied.  Chunks lie at fixed distances from the
 // first visible key, so a chunk's partial result does not depend on how many chunks there are.
 GB_API int gb_sink_attention_chunks(int n, int H, int G, int window, int max_ctx, int* chunk_out) {
+  // (`window`: the most keys a windowed position sees, the kept first positions included)
   const int group = H / (G > 0 ? G : 1);
   const int blocks = n * G * gb_div_up(group, SA_WARPS);
   int wanted = 592 / (blocks > 0 ? blocks : 1);
@@ -390,17 +426,19 @@ GB_OP(gb_op_embed_scaled) {
 // (heads of `dim` entries side by side in one query or key head; 0 means 1); flags bit 0: norm over the whole
 // projection (gains as long as the projection), bit 1: q out is bfloat16 (else 32-bit), bit 2: the pages are bfloat16,
 // bit 3: norm over every head of `dim` entries (gains of `dim` entries, shared), bit 4: the rotation pairs entry i
-// with entry i + rot_dims / 2 (else adjacent entries); f0 eps
+// with entry i + rot_dims / 2 (else adjacent entries), bit 5: every head of `dim` entries is divided by its root mean
+// square AFTER the rotation, without a gain; f0 eps
 GB_OP(gb_op_qk_prep) {
   const int n = (int)a[16], H = (int)a[17], G = (int)a[18], dim = (int)a[19], vdim = (int)a[20];
   const int maps = a[22] > 0 ? (int)a[22] : 1;
   if (n <= 0) return 0;
   if (a[7] % 2 || a[7] > dim) GB_FAIL(GB_ERR_ARG, "qk_prep: %lld rotated dimensions of %d", a[7], dim);
   if (G <= 0 || H % G) GB_FAIL(GB_ERR_ARG, "qk_prep: %d heads over %d kv heads", H, G);
-  if ((flags & PREP_NORM_WHOLE) && (flags & PREP_NORM_HEAD)) GB_FAIL(GB_ERR_ARG, "qk_prep: one kind of norm at a time");
+  if (((flags & PREP_NORM_WHOLE) ? 1 : 0) + ((flags & PREP_NORM_HEAD) ? 1 : 0) + ((flags & PREP_NORM_AFTER) ? 1 : 0) > 1)
+    GB_FAIL(GB_ERR_ARG, "qk_prep: one kind of norm at a time");
   const int threads = H * maps * dim >= 2048 ? 512 : 256;
   const long long ldq = (long long)H * maps * dim;
-  const int mode = flags & (PREP_NORM_WHOLE | PREP_NORM_HEAD | PREP_ROT_HALVES);
+  const int mode = flags & (PREP_NORM_WHOLE | PREP_NORM_HEAD | PREP_ROT_HALVES | PREP_NORM_AFTER);
 #define PREP(TC, TQ)                                                                                                     \
   gb_launch(qk_prep_kernel<TC, TQ>, dim3(n), dim3(threads), 0, ctx->stream, op_ptr<const float>(a[0]), a[1], (int)a[2],    \
             (int)a[3], op_ptr<const float>(a[4]), op_ptr<const float>(a[5]), op_ptr<const float>(a[6]), (int)a[7],        \
@@ -423,7 +461,8 @@ GB_OP(gb_op_qk_prep) {
 // share the value; every map is a softmax of its own and has an output of its own;
 // flags bit 0: the softmax has a sink, bit 1: q is bfloat16 (else 32-bit), bit 2: the pages are, bit 3: out is,
 // bit 4: position p sees the positions of its own block of `window` positions, counted from 0, up to p (else
-// the last `window`); f0 scale, f1 soft cap (0: none)
+// the last `window`); a22 a learned score of the sink per head (f32 [heads]) or 0: the sink's score is 0;
+// f0 scale, f1 soft cap (0: none), f2 keep_first: a windowed position also sees the positions below this number
 GB_OP(gb_op_sink_attention) {
   const int n = (int)a[13], G = (int)a[15], dim = (int)a[16], vdim = (int)a[17];
   const int maps = a[21] > 0 ? (int)a[21] : 1;
@@ -433,13 +472,17 @@ GB_OP(gb_op_sink_attention) {
   if (vdim > 256) GB_FAIL(GB_ERR_ARG, "sink_attention: values of %d entries (at most 256)", vdim);
   const int group = H / G, sink = flags & 1, blocked = (flags & 16) ? 1 : 0;
   if (blocked && a[18] <= 0) GB_FAIL(GB_ERR_ARG, "sink_attention: blocks of %lld positions", a[18]);
+  const int keep_first = a[18] > 0 ? (int)f[2] : 0;
+  if (keep_first < 0 || (keep_first > 0 && blocked)) GB_FAIL(GB_ERR_ARG, "sink_attention: %d kept first positions", keep_first);
+  if (a[22] && !sink) GB_FAIL(GB_ERR_ARG, "sink_attention: learned sink scores without a sink");
+  const float* sink_scores = op_ptr<const float>(a[22]);
   const int warps = group < SA_WARPS ? group : SA_WARPS;
   const int hb = gb_div_up(group, SA_WARPS);
   const int KS = (maps * dim) | 1;
   const size_t smem = sizeof(long long) * SA_KT + sizeof(float) * ((size_t)warps * dim + (size_t)SA_KT * (KS + vdim));
   if (smem > 200 * 1024) GB_FAIL(GB_ERR_ARG, "sink_attention: heads of %d entries need %zu bytes of shared memory", dim, smem);
   int chunk = 0;
-  int splits = gb_sink_attention_chunks(n, H, G, (int)a[18], (int)a[19], &chunk);
+  int splits = gb_sink_attention_chunks(n, H, G, a[18] > 0 ? (int)a[18] + keep_first : 0, (int)a[19], &chunk);
   float* ws = op_ptr<float>(a[20]);
   if (ws == nullptr || (long long)n * H * splits > SA_WS_ROWS) splits = 1;
   const dim3 grid(n, G * hb, splits), block(32 * warps);
@@ -455,7 +498,7 @@ GB_OP(gb_op_sink_attention) {
               (long long)H * dim, op_ptr<const TC>(a[1]), op_ptr<const TC>(a[2]), op_ptr<const int>(a[3]), (int)a[4],    \
               (int)a[5], (int)a[6], op_ptr<const int>(a[7]), op_ptr<const int>(a[8]), op_ptr<const float>(a[9]), a[10],  \
               op_ptr<TO>(a[11]), a[12], H, G, dim, vdim, (float)f[0], (float)f[1], (int)a[18], sink, splits, chunk, ws,  \
-              maps, blocked, ctx->status);                                                                              \
+              maps, blocked, sink_scores, keep_first, ctx->status);                                                    \
   } while (0)
 #define SA_VR(TC, TQ, TO)                                                                                               \
   do {                                                                                                                  \
@@ -473,6 +516,6 @@ GB_OP(gb_op_sink_attention) {
   GB_CHECK_LAUNCH("sink_attention");
   if (splits == 1) return 1;
   const int rc = gb_sink_attention_merge(ws, splits, op_ptr<const float>(a[9]), a[10], op_ptr<void>(a[11]), ob ? 1 : 0, a[12],
-                                         n, H, vdim, sink, ctx->stream);
+                                         n, H, vdim, sink, sink_scores, maps, ctx->stream);
   return rc < 0 ? rc : 2;
 }

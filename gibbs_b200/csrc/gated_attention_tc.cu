@@ -78,6 +78,8 @@ struct TcParams {
   int N, R, H, G, tokens_per_tile, maps, blocked;
   float scale, softcap;
   int window, sink, splits, chunk;
+  const float* sink_scores;      // a learned score of the sink per head, or null: 0
+  int keep_first;                // a windowed position also sees the positions below this number
   float* ws; int* status;
 };
 
@@ -112,8 +114,14 @@ __global__ void __launch_bounds__(TC_THREADS, (DK + DV <= 128) ? 4 : 2) sink_att
   const int* table = p.block_table + (size_t)p.tok_req[t0] * p.bt_stride;
   const int n_rows = n_tok * group;
   const int lo = p.window > 0 ? (p.blocked ? (pos0 / p.window) * p.window : max(0, pos0 - p.window + 1)) : 0;
-  const int k_begin = p.splits > 1 ? lo + (int)blockIdx.z * p.chunk : lo;
-  const int k_end = p.splits > 1 ? min(pos0 + n_tok - 1, k_begin + p.chunk - 1) : pos0 + n_tok - 1;
+  // the keys the tile may see, in order: the first `kept` positions of the sequence that lie in front of the first
+  // token's window, then lo .. the last token's position; key number v of this list is position v (v < kept) or
+  // v + shift
+  const int kept = (p.window > 0 && !p.blocked) ? min(p.keep_first, lo) : 0;
+  const int shift = lo - kept;
+  const int k_last = kept + pos0 + n_tok - 1 - lo;
+  const int k_begin = p.splits > 1 ? (int)blockIdx.z * p.chunk : 0;
+  const int k_end = p.splits > 1 ? min(k_last, k_begin + p.chunk - 1) : k_last;
   const int n_tiles = k_end >= k_begin ? (k_end - k_begin) / TC_KT + 1 : 0;
 
   // two threads a key row: the row's page is looked up once, each thread copies half of the row's 16-byte pieces
@@ -123,9 +131,10 @@ __global__ void __launch_bounds__(TC_THREADS, (DK + DV <= 128) ? 4 : 2) sink_att
     bf16* kd = Ks + buf * TC_KT * KS;
     bf16* vd = Vs + buf * TC_KT * VS;
     const int j = tid >> 1, first = (tid & 1) * HALF;
-    const int kp = k0 + j;
+    const int kv = k0 + j;
+    const int kp = kv < kept ? kv : kv + shift;
     long long row = -1;
-    if (kp <= k_end) {
+    if (kv <= k_end) {
       const int page = table[kp / p.page_size];
       if (page < 0 || page >= p.n_pages) atomicExch(p.status, STATUS_BAD_PAGE_READ);
       else row = ((long long)page * p.G + g) * p.page_size + kp % p.page_size;
@@ -194,8 +203,12 @@ __global__ void __launch_bounds__(TC_THREADS, (DK + DV <= 128) ? 4 : 2) sink_att
       const bf16* vb = Vs + (it & 1) * TC_KT * VS;
       const int k0 = k_begin + it * TC_KT;
       // every row of the tile sees every key of this key tile: nothing to mask
-      const bool all_seen = k0 + TC_KT - 1 <= min(pos0, k_end) && n_rows - rb >= 16 &&
-                            (p.window <= 0 || (p.blocked ? k0 >= (pos_last / p.window) * p.window : k0 > pos_last - p.window));
+      // (k0 counts visible keys; kr is the position of the tile's first key when the tile lies behind the kept ones)
+      const int kr = k0 + shift;
+      const bool all_seen = n_rows - rb >= 16 && k0 + TC_KT - 1 <= k_end &&
+                            (k0 + TC_KT <= kept ||
+                             (k0 >= kept && kr + TC_KT - 1 <= pos0 &&
+                              (p.window <= 0 || (p.blocked ? kr >= (pos_last / p.window) * p.window : kr > pos_last - p.window))));
       float s[2 * NB][4];
 #pragma unroll
       for (int n = 0; n < 2 * NB; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
@@ -220,9 +233,10 @@ __global__ void __launch_bounds__(TC_THREADS, (DK + DV <= 128) ? 4 : 2) sink_att
           float v = s[n][e] * c_in;
           if (capped) v = fmaf(c_mul, tc_rcp(tc_ex2(v) + 1.f), c_add);
           if (!all_seen) {
-            const int kp = kcol + (e & 1);
+            const int kv = kcol + (e & 1);
+            const int kp = kv < kept ? kv : kv + shift;
             const int pos = e < 2 ? pos_lo : pos_hi, first = e < 2 ? first_lo : first_hi;
-            if (kp > pos || kp < first || kp > k_end) v = -INFINITY;
+            if (kp > pos || (kp < first && kp >= p.keep_first) || kv > k_end) v = -INFINITY;
           }
           s[n][e] = v;
           if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
@@ -315,9 +329,10 @@ __global__ void __launch_bounds__(TC_THREADS, (DK + DV <= 128) ? 4 : 2) sink_att
         w[2 + d] = acc;
         continue;
       }
-      const float M = p.sink ? fmaxf(m, 0.f) : m;
+      const float z = p.sink_scores ? p.sink_scores[h / p.maps] : 0.f;
+      const float M = p.sink ? fmaxf(m, z) : m;
       const float e = expf(m - M);
-      const float inv = 1.0f / fmaf(e, l, p.sink ? expf(0.f - M) : 0.f);
+      const float inv = 1.0f / fmaf(e, l, p.sink ? expf(z - M) : 0.f);
       const float gt = p.gate ? hy_sigmoid(p.gate[(size_t)t * p.ld_gate + (size_t)h * DV + d]) : 1.f;
       const float val = fmaf(e, acc, 0.f) * inv * gt;
       if (p.out_f32) p.out_f32[(size_t)t * p.ldo + (size_t)h * DV + d] = val;
@@ -343,9 +358,10 @@ __global__ void __launch_bounds__(TC_THREADS, (DK + DV <= 128) ? 4 : 2) sink_att
       continue;
     }
     // (the same arithmetic as the merge of chunks: one chunk, and the sink)
-    const float M = p.sink ? fmaxf(m, 0.f) : m;
+    const float z = p.sink_scores ? p.sink_scores[h / p.maps] : 0.f;
+    const float M = p.sink ? fmaxf(m, z) : m;
     const float e = expf(m - M);
-    const float inv = 1.0f / fmaf(e, l, p.sink ? expf(0.f - M) : 0.f);
+    const float inv = 1.0f / fmaf(e, l, p.sink ? expf(z - M) : 0.f);
     const float* gt = p.gate ? p.gate + (size_t)t * p.ld_gate + (size_t)h * DV : nullptr;
     const size_t at = (size_t)t * p.ldo + (size_t)h * DV;
 #pragma unroll
@@ -376,7 +392,8 @@ int launch_tc(const TcParams& p, dim3 grid, cudaStream_t stream) {
 
 // (gated_attention.cu)
 int gb_sink_attention_merge(const float* ws, int splits, const float* gate, long long ld_gate, void* out, int out_bf16,
-                            long long ldo, int n, int H, int vdim, int sink, cudaStream_t stream);
+                            long long ldo, int n, int H, int vdim, int sink, const float* sink_scores, int maps,
+                            cudaStream_t stream);
 extern "C" int gb_sink_attention_workspace_rows();
 
 // Whether the tensor-core kernel takes these sizes (keys and values of 32 to 128 entries in steps of 32, up to
@@ -395,8 +412,9 @@ GB_API int gb_sink_attention_tc_supported(int heads, int kv_heads, int dim, int 
 // workspace for partial results (gb_sink_attention_workspace_rows() rows of vdim + 2 floats) or 0, a21 requests, a22
 // row of each request's first token [requests]; flags bit 0: the softmax has a sink, bit 1: out is 32-bit (else
 // bfloat16), bit 2: a position sees its own block of `window` positions, counted from 0, bits 8 to 11: maps (0 means
-// 1): q is [tokens, heads * maps * dim], a key row [maps * dim], out [tokens, heads * maps * vdim]; f0 scale, f1 soft
-// cap (0: none)
+// 1): q is [tokens, heads * maps * dim], a key row [maps * dim], out [tokens, heads * maps * vdim]; a23 a learned score
+// of the sink per head (f32 [heads]) or 0: the sink's score is 0; f0 scale, f1 soft cap (0: none), f2 keep_first: a
+// windowed position also sees the positions below this number
 GB_OP(gb_op_sink_attention_tc) {
   const int n = (int)a[13], H = (int)a[14], G = (int)a[15], dim = (int)a[16], vdim = (int)a[17], R = (int)a[21];
   if (n <= 0 || R <= 0) return 0;
@@ -423,12 +441,16 @@ GB_OP(gb_op_sink_attention_tc) {
   p.N = n; p.R = R; p.H = H; p.G = G; p.tokens_per_tile = narrow ? 1 : TC_ROWS / group;
   p.scale = (float)f[0]; p.softcap = (float)f[1];
   p.window = (int)a[18]; p.sink = flags & 1;
+  p.sink_scores = op_ptr<const float>(a[23]);
+  p.keep_first = (p.window > 0 && !p.blocked) ? (int)f[2] : 0;
+  if (p.keep_first < 0) GB_FAIL(GB_ERR_ARG, "sink_attention_tc: %d kept first positions", p.keep_first);
+  if (p.sink_scores && !p.sink) GB_FAIL(GB_ERR_ARG, "sink_attention_tc: learned sink scores without a sink");
   p.ws = op_ptr<float>(a[20]); p.status = ctx->status;
   // at most this many tiles: every request may end with a partial one
   const int tiles = narrow ? n : gb_div_up(n, p.tokens_per_tile) + R;
   // chunks of keys when the tiles alone leave the GPU idle (decoding); whole key tiles, at fixed distances from the
   // first visible key; with a window the cut depends on the launch's sizes only
-  const int span = p.window > 0 ? p.window + p.tokens_per_tile : (a[19] > 0 ? (int)a[19] : 1);
+  const int span = p.window > 0 ? p.window + p.keep_first + p.tokens_per_tile : (a[19] > 0 ? (int)a[19] : 1);
   int wanted = 592 / (tiles * G * maps);
   if (wanted > 32) wanted = 32;
   p.splits = 1; p.chunk = span;
@@ -459,6 +481,6 @@ GB_OP(gb_op_sink_attention_tc) {
   if (rc < 0) return rc;
   if (p.splits == 1) return 1;
   rc = gb_sink_attention_merge(p.ws, p.splits, p.gate, p.ld_gate, out_f32 ? (void*)p.out_f32 : (void*)p.out, out_f32 ? 0 : 1,
-                               p.ldo, n, H * maps, vdim, p.sink, ctx->stream);
+                               p.ldo, n, H * maps, vdim, p.sink, p.sink_scores, maps, ctx->stream);
   return rc < 0 ? rc : 2;
 }

@@ -25,7 +25,8 @@ enum { STATUS_BAD_PAGE_WRITE = 1, STATUS_BAD_PAGE_READ = 2 };
 
 // one block per token: warp 0 writes the cache row, the others rotate the heads' queries
 template <typename TC>
-__global__ void latent_prep_kernel(const float* fused, long long ld, int dkv_col, const float* __restrict__ gain,
+__global__ void latent_prep_kernel(const float* fused, long long ld, int dkv_col, const float* queries, long long ldq,
+                                   const float* __restrict__ gain,
                                    const float* __restrict__ inv_freq, int rot_dims, const int* tok_req,
                                    const int* tok_pos, const int* block_table, int bt_stride, int page_size, TC* pages,
                                    int n_pages, int H, int dn, int dr, int r, float* qp, float eps, int* status) {
@@ -61,7 +62,7 @@ __global__ void latent_prep_kernel(const float* fused, long long ld, int dkv_col
   const int w0 = warps > 1 ? 1 : 0, step = warps > 1 ? warps - 1 : 1;
   if (warps > 1 && warp == 0) return;
   for (int h = warp - w0; h < H; h += step) {
-    const float* q = row + (size_t)h * (dn + dr) + dn;
+    const float* q = queries + (size_t)t * ldq + (size_t)h * (dn + dr) + dn;
     float* o = qp + ((size_t)t * H + h) * (r + dr) + r;
     for (int j = lane; j < half; j += 32) {
       const float ang = (float)pos * inv_freq[j];
@@ -76,7 +77,7 @@ __global__ void latent_prep_kernel(const float* fused, long long ld, int dkv_col
 
 template <typename TW, typename TO>
 __global__ void head_linear_kernel(const float* x, long long ldx, long long xh, const TW* __restrict__ W, TO* out,
-                                   long long ldo, long long oh, int n, int O, int I) {
+                                   long long ldo, long long oh, int n, int O, int I, const float* gate, long long ld_gate) {
   pdl_trigger();
   pdl_wait();
   const int h = blockIdx.z, r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
@@ -94,7 +95,10 @@ __global__ void head_linear_kernel(const float* x, long long ldx, long long xh, 
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       const int col = c0 + tx * 4 + c;
-      if (col < O) out[(size_t)row * ldo + (size_t)h * oh + col] = from_f32<TO>(acc[r][c]);
+      if (col < O) {
+        const float gt = gate ? hy_sigmoid(gate[(size_t)row * ld_gate + (size_t)h * oh + col]) : 1.f;
+        out[(size_t)row * ldo + (size_t)h * oh + col] = from_f32<TO>(gate ? acc[r][c] * gt : acc[r][c]);
+      }
     }
   }
 }
@@ -105,7 +109,8 @@ constexpr int HL_SMALL_ROWS = 16;
 
 template <typename TW, typename TO>
 __global__ void head_linear_small_kernel(const float* x, long long ldx, long long xh, const TW* __restrict__ W, TO* out,
-                                         long long ldo, long long oh, int n, int O, int I) {
+                                         long long ldo, long long oh, int n, int O, int I, const float* gate,
+                                         long long ld_gate) {
   extern __shared__ float xs[];                          // [n][I]
   pdl_trigger();
   pdl_wait();
@@ -132,7 +137,10 @@ __global__ void head_linear_small_kernel(const float* x, long long ldx, long lon
     for (int t = 0; t < HL_SMALL_ROWS; ++t) {
       if (t < n) {
         const float v = warp_sum(acc[t]);
-        if (lane == 0) out[(size_t)t * ldo + (size_t)h * oh + o] = from_f32<TO>(v);
+        if (lane == 0) {
+          const float gt = gate ? hy_sigmoid(gate[(size_t)t * ld_gate + (size_t)h * oh + o]) : 1.f;
+          out[(size_t)t * ldo + (size_t)h * oh + o] = from_f32<TO>(gate ? v * gt : v);
+        }
       }
     }
   }
@@ -383,7 +391,8 @@ __global__ void latent_attention_merge_kernel(const float* ws, int splits, const
 
 bool gb_head_linear_tc_takes(int n, int I, long long ldx, long long xh, const void* x, const void* W);
 void gb_head_linear_tc_launch(const float* x, long long ldx, long long xh, const bf16* W, void* out, bool out_bf16,
-                              long long ldo, long long oh, int n, int H, int O, int I, cudaStream_t stream);
+                              long long ldo, long long oh, int n, int H, int O, int I, const float* gate, long long ld_gate,
+                              cudaStream_t stream);
 bool gb_latent_attention_tc_takes(int n, int R, int H, int r, int dr, int window, bool pages_bf16, const void* pages,
                                   const void* qp, const void* out, long long ldo);
 int gb_latent_attention_tc_launch(const float* qp, const bf16* pages, const int* block_table, int bt_stride, int page_size,
@@ -420,7 +429,8 @@ GB_API int gb_latent_attention_workspace_rows() { return LA_HB * 2 * (592 + 592)
 // a3 gain of the latent's norm [r], a4 inv_freq [rot_dims / 2], a5 rot_dims, a6 token -> request, a7 token ->
 // position, a8 block table, a9 its entries per request, a10 page size, a11 pages, a12 number of pages, a13 their dtype,
 // a14 tokens, a15 heads, a16 plain query size, a17 rotated size, a18 latent size, a19 q' [tokens, heads, r + rot]
-// (f32); f0 eps
+// (f32), a20 the queries [tokens, heads * (plain + rotated)] (f32) when they are no part of the fused rows (they came
+// through a product of their own), else 0, a21 their row stride; f0 eps
 GB_OP(gb_op_latent_prep) {
   const int n = (int)a[14], H = (int)a[15];
   if (n <= 0) return 0;
@@ -428,7 +438,8 @@ GB_OP(gb_op_latent_prep) {
   const int warps = H + 1 < 8 ? H + 1 : 8;
 #define PREP(TC)                                                                                                       \
   gb_launch(latent_prep_kernel<TC>, dim3(n), dim3(32 * warps), 0, ctx->stream, op_ptr<const float>(a[0]), a[1], (int)a[2], \
-            op_ptr<const float>(a[3]), op_ptr<const float>(a[4]), (int)a[5], op_ptr<const int>(a[6]),                   \
+            a[20] ? op_ptr<const float>(a[20]) : op_ptr<const float>(a[0]), a[20] ? a[21] : a[1], op_ptr<const float>(a[3]), \
+            op_ptr<const float>(a[4]), (int)a[5], op_ptr<const int>(a[6]),                   \
             op_ptr<const int>(a[7]), op_ptr<const int>(a[8]), (int)a[9], (int)a[10], op_ptr<TC>(a[11]), (int)a[12], H,  \
             (int)a[16], (int)a[17], (int)a[18], op_ptr<float>(a[19]), (float)f[0], ctx->status)
   if (a[13] == GB_BF16) PREP(bf16); else PREP(float);
@@ -438,15 +449,16 @@ GB_OP(gb_op_latent_prep) {
 }
 
 // a0 x (f32), a1 its row stride, a2 elements between heads in a row, a3 W [H, O, I], a4 its dtype, a5 out, a6 its
-// dtype, a7 its row stride, a8 elements between heads in a row, a9 rows, a10 heads, a11 O, a12 I; flags bit 0: the
-// generic kernels whatever the sizes
+// dtype, a7 its row stride, a8 elements between heads in a row, a9 rows, a10 heads, a11 O, a12 I, a13 gate logits
+// (f32, one per output element, laid out like a row of out) or 0: the outputs are multiplied by their sigmoid, a14
+// their row stride; flags bit 0: the generic kernels whatever the sizes
 GB_OP(gb_op_head_linear) {
   const int n = (int)a[9], H = (int)a[10], O = (int)a[11], I = (int)a[12];
   if (n <= 0) return 0;
   if (a[4] == GB_BF16 && !(flags & 1) &&
       gb_head_linear_tc_takes(n, I, a[1], a[2], op_ptr<const void>(a[0]), op_ptr<const void>(a[3]))) {
     gb_head_linear_tc_launch(op_ptr<const float>(a[0]), a[1], a[2], op_ptr<const bf16>(a[3]), op_ptr<void>(a[5]),
-                             a[6] == GB_BF16, a[7], a[8], n, H, O, I, ctx->stream);
+                             a[6] == GB_BF16, a[7], a[8], n, H, O, I, op_ptr<const float>(a[13]), a[14], ctx->stream);
     GB_CHECK_LAUNCH("head_linear (tensor cores)");
     return 1;
   }
@@ -457,10 +469,10 @@ GB_OP(gb_op_head_linear) {
 #define HL(TW, TO)                                                                                                  \
   if (small)                                                                                                        \
     gb_launch(head_linear_small_kernel<TW, TO>, grid, block, smem, ctx->stream, op_ptr<const float>(a[0]), a[1], a[2], \
-              op_ptr<const TW>(a[3]), op_ptr<TO>(a[5]), a[7], a[8], n, O, I);                                        \
+              op_ptr<const TW>(a[3]), op_ptr<TO>(a[5]), a[7], a[8], n, O, I, op_ptr<const float>(a[13]), a[14]);     \
   else                                                                                                              \
     gb_launch(head_linear_kernel<TW, TO>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], a[2],       \
-              op_ptr<const TW>(a[3]), op_ptr<TO>(a[5]), a[7], a[8], n, O, I)
+              op_ptr<const TW>(a[3]), op_ptr<TO>(a[5]), a[7], a[8], n, O, I, op_ptr<const float>(a[13]), a[14])
   if (a[4] == GB_BF16) { if (a[6] == GB_BF16) { HL(bf16, bf16); } else { HL(bf16, float); } }
   else { if (a[6] == GB_BF16) { HL(float, bf16); } else { HL(float, float); } }
 #undef HL

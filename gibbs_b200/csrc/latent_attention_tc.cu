@@ -289,7 +289,8 @@ constexpr int HLT_STRIDE = 40;     // bfloat16 entries a row of a 64 x 32 tile t
 template <typename TO>
 __global__ void __launch_bounds__(128) head_linear_tc_kernel(const float* x, long long ldx, long long xh,
                                                              const bf16* __restrict__ W, TO* out, long long ldo,
-                                                             long long oh, int n, int O, int I) {
+                                                             long long oh, int n, int O, int I, const float* gate,
+                                                             long long ld_gate) {
   __shared__ __align__(16) bf16 As[64 * HLT_STRIDE];
   __shared__ __align__(16) bf16 Bs[64 * HLT_STRIDE];
   pdl_trigger();
@@ -357,11 +358,13 @@ __global__ void __launch_bounds__(128) head_linear_tc_kernel(const float* x, lon
     const int row = r0 + wm * 16 + g + 8 * half;
     if (row >= n) continue;
     TO* dst = out + (size_t)row * ldo + (size_t)h * oh;
+    // (a gate logit per output element, laid out like the outputs of a row)
+    const float* gt = gate ? gate + (size_t)row * ld_gate + (size_t)h * oh : nullptr;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int col = c0 + 8 * j + 2 * t4;
-      if (col < O) dst[col] = from_f32<TO>(acc[j][2 * half]);
-      if (col + 1 < O) dst[col + 1] = from_f32<TO>(acc[j][2 * half + 1]);
+      if (col < O) dst[col] = from_f32<TO>(gt ? acc[j][2 * half] * hy_sigmoid(gt[col]) : acc[j][2 * half]);
+      if (col + 1 < O) dst[col + 1] = from_f32<TO>(gt ? acc[j][2 * half + 1] * hy_sigmoid(gt[col + 1]) : acc[j][2 * half + 1]);
     }
   }
 }
@@ -375,12 +378,15 @@ bool gb_head_linear_tc_takes(int n, int I, long long ldx, long long xh, const vo
 }
 
 void gb_head_linear_tc_launch(const float* x, long long ldx, long long xh, const bf16* W, void* out, bool out_bf16,
-                              long long ldo, long long oh, int n, int H, int O, int I, cudaStream_t stream) {
+                              long long ldo, long long oh, int n, int H, int O, int I, const float* gate,
+                              long long ld_gate, cudaStream_t stream) {
   const dim3 grid(gb_div_up(O, 64), gb_div_up(n, 64), H), block(128);
   if (out_bf16)
-    gb_launch(head_linear_tc_kernel<bf16>, grid, block, 0, stream, x, ldx, xh, W, static_cast<bf16*>(out), ldo, oh, n, O, I);
+    gb_launch(head_linear_tc_kernel<bf16>, grid, block, 0, stream, x, ldx, xh, W, static_cast<bf16*>(out), ldo, oh, n, O, I,
+              gate, ld_gate);
   else
-    gb_launch(head_linear_tc_kernel<float>, grid, block, 0, stream, x, ldx, xh, W, static_cast<float*>(out), ldo, oh, n, O, I);
+    gb_launch(head_linear_tc_kernel<float>, grid, block, 0, stream, x, ldx, xh, W, static_cast<float*>(out), ldo, oh, n, O, I,
+              gate, ld_gate);
 }
 
 // Whether the tensor-core kernel takes a launch: bfloat16 pages whose rows can be copied in 16-byte pieces, no rotated

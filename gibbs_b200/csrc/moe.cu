@@ -56,13 +56,15 @@ __global__ void moe_route_kernel(const float* logits, long long ld, int n, int E
   if (shared_gate && lane == 0) shared_gate[t] = hy_sigmoid(z[shared_col]);
 }
 
-// One warp per token.  scores: 0 sigmoid(z), 1 softmax(z) over all `n_out` router outputs.  The choice is made on
+// One warp per token.  scores: 0 sigmoid(z), 1 softmax(z) over all `n_out` router outputs, 2 the logits z themselves.
+// `normalise`: 0 a chosen output's weight is its score, 1 the score divided by the sum of the chosen scores, 2 the
+// softmax over the chosen scores alone.  The choice is made on
 // score + correction; with `groups` > 1 the outputs form that many equal groups of neighbours, a group's mark is
 // its largest choice score, and only outputs of the `keep` best groups can be chosen.  The weight of a chosen
 // output is its score without the correction, not renormalised.  Ties go to the lower index.
 __global__ void moe_route_grouped_kernel(const float* logits, long long ld, int n, int n_out, int top, int scores,
                                          const float* __restrict__ correction, int groups, int keep, int* idx,
-                                         float* weight) {
+                                         float* weight, int normalise) {
   extern __shared__ float route_sm[];                    // per warp: scores [n_out], choice scores [n_out], group marks
   pdl_trigger();
   pdl_wait();
@@ -85,6 +87,8 @@ __global__ void moe_route_grouped_kernel(const float* logits, long long ld, int 
     }
     sum = warp_sum(sum);
     for (int e = lane; e < n_out; e += 32) s[e] = s[e] / sum;
+  } else if (scores == 2) {
+    for (int e = lane; e < n_out; e += 32) s[e] = z[e];
   } else {
     for (int e = lane; e < n_out; e += 32) s[e] = hy_sigmoid(z[e]);
   }
@@ -140,6 +144,20 @@ __global__ void moe_route_grouped_kernel(const float* logits, long long ld, int 
       c[be] = -INFINITY;                                   // taken
     }
     __syncwarp();
+  }
+  if (normalise && lane == 0) {
+    float* w = weight + (size_t)t * top;
+    float sum = 0.f;
+    if (normalise == 2) {
+      const float mx = w[0];                                // (the first choice has the largest score)
+      for (int k = 0; k < top; ++k) {
+        w[k] = expf(w[k] - mx);
+        sum += w[k];
+      }
+    } else {
+      for (int k = 0; k < top; ++k) sum += w[k];
+    }
+    for (int k = 0; k < top; ++k) w[k] = w[k] / sum;
   }
 }
 
@@ -295,8 +313,9 @@ __global__ void moe_combine_weighted_kernel(const float* out, long long ldo, con
 }  // namespace
 
 // a0 logits (f32), a1 their row stride, a2 tokens, a3 router outputs (experts and identity outputs), a4 top, a5 scores
-// (0 sigmoid, 1 softmax), a6 correction [outputs] (f32) or 0, a7 groups (1: none), a8 groups kept, a9 chosen outputs
-// [tokens, top] (int32), a10 their weights (f32)
+// (0 sigmoid, 1 softmax, 2 the logits), a6 correction [outputs] (f32) or 0, a7 groups (1: none), a8 groups kept, a9 chosen
+// outputs [tokens, top] (int32), a10 their weights (f32), a11 how the chosen scores become weights: 0 as they are, 1
+// divided by their sum, 2 their softmax
 GB_OP(gb_op_moe_route_grouped) {
   const int n = (int)a[2], n_out = (int)a[3], top = (int)a[4];
   int groups = (int)a[7], keep = (int)a[8];
@@ -311,7 +330,7 @@ GB_OP(gb_op_moe_route_grouped) {
   const size_t smem = sizeof(float) * warps * (2 * (size_t)n_out + groups);
   gb_launch(moe_route_grouped_kernel, dim3(gb_div_up(n, warps)), dim3(32 * warps), smem, ctx->stream,
             op_ptr<const float>(a[0]), a[1], n, n_out, top, (int)a[5], op_ptr<const float>(a[6]), groups, keep,
-            op_ptr<int>(a[9]), op_ptr<float>(a[10]));
+            op_ptr<int>(a[9]), op_ptr<float>(a[10]), (int)a[11]);
   GB_CHECK_LAUNCH("moe_route_grouped");
   return 1;
 }

@@ -7,7 +7,8 @@
 //  gb_op_gelu_mul_rows   g = gelu_tanh(g) * table[id, offset : offset + dim] (a per-token input)
 //  gb_op_gated_group_norm  out = rmsnorm_in_groups(y * silu(z)) * gain
 //  gb_op_act_rows        out = act(x), act one of gelu (erf), gelu (tanh), silu, relu: the unit of a feed-forward
-//                        without a gate
+//                        without a gate; or out = act(g) * u for rows [g | u]: a gated unit
+//  gb_op_scaled_sum      x += mult * (s1 * y1 + s2 * y2): two sublayers' outputs, scaled per channel, into the stream
 //  gb_op_head_norm       per head: out = rmsnorm(x - lambda * x2) * gain * sigmoid(gate) * factor, each of x2,
 //                        gain and gate optional: the norm behind a recurrence or behind two attention maps
 #include "hybrid.cuh"
@@ -237,6 +238,63 @@ __global__ void norm_add_kernel(float* x, long long ldx, const float* y, long lo
   }
 }
 
+// x[t, :] += mult * (s1 * y1[t, :] + s2 * y2[t, :]): the residual sum of an arrangement whose sublayers read the same
+// normed rows and whose outputs are scaled channel by channel before they are added (y2, s2: optional).  `then`: the
+// norm in front of the NEXT layer, taken of the new rows while they are in registers.
+__global__ void scaled_sum_kernel(float* x, long long ldx, const float* y1, long long ld1, const float* __restrict__ s1,
+                                  const float* y2, long long ld2, const float* __restrict__ s2, int dim, float mult,
+                                  ThenNorm then) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  float* o = x + (size_t)blockIdx.x * ldx;
+  const float* a = y1 + (size_t)blockIdx.x * ld1;
+  const float* b = y2 ? y2 + (size_t)blockIdx.x * ld2 : nullptr;
+  pdl_wait();
+  RowCache c;
+  c.whole = dim <= NORM_CACHE * (int)blockDim.x;
+  if (c.whole) {
+#pragma unroll
+    for (int i = 0; i < NORM_CACHE; ++i) {
+      const int d = threadIdx.x + i * blockDim.x;
+      float v = 0.f;
+      if (d < dim) {
+        float sum = s1[d] * a[d];
+        if (b) sum = fmaf(s2[d], b[d], sum);
+        v = fmaf(mult, sum, o[d]);
+        o[d] = v;
+      }
+      c.v[i] = v;
+    }
+  } else {
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+      float sum = s1[d] * a[d];
+      if (b) sum = fmaf(s2[d], b[d], sum);
+      o[d] = fmaf(mult, sum, o[d]);
+    }
+  }
+  if (then.gain == nullptr) return;
+  if (!c.whole) __syncthreads();                          // (the row is read again from memory)
+  float mean2, rstd2;
+  row_stats(o, c, dim, then.kind, then.eps, scratch, mean2, rstd2);
+  if (c.whole) {
+#pragma unroll
+    for (int i = 0; i < NORM_CACHE; ++i) {
+      const int d = threadIdx.x + i * blockDim.x;
+      if (d < dim) {
+        const float h = (c.v[i] - mean2) * rstd2 * then.gain[d];
+        if (then.out_dtype == GB_BF16) ((bf16*)then.out)[(size_t)blockIdx.x * dim + d] = __float2bfloat16_rn(h);
+        else ((float*)then.out)[(size_t)blockIdx.x * dim + d] = h;
+      }
+    }
+  } else {
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+      const float h = (o[d] - mean2) * rstd2 * then.gain[d];
+      if (then.out_dtype == GB_BF16) ((bf16*)then.out)[(size_t)blockIdx.x * dim + d] = __float2bfloat16_rn(h);
+      else ((float*)then.out)[(size_t)blockIdx.x * dim + d] = h;
+    }
+  }
+}
+
 template <typename TO>
 __global__ void clamped_glu_kernel(const float* gu, long long ld, TO* out, long long ldo, int n, int inner, float alpha,
                                    float limit, float up_add) {
@@ -300,26 +358,34 @@ __device__ __forceinline__ float act_value(float z, int kind) {
 }
 
 template <typename TO>
-__global__ void act_rows_kernel(const float* x, long long ld, TO* out, long long ldo, int n, int inner, int kind) {
+__global__ void act_rows_kernel(const float* x, long long ld, TO* out, long long ldo, int n, int inner, int kind,
+                                int up) {
   pdl_trigger();
   pdl_wait();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long long)n * inner) return;
   const int t = (int)(i / inner), c = (int)(i - (long long)t * inner);
-  out[(size_t)t * ldo + c] = from_f32<TO>(act_value(x[(size_t)t * ld + c], kind));
+  const float v = act_value(x[(size_t)t * ld + c], kind);
+  // (`up` > 0: a gated unit whose second factor lies `up` columns further in the row)
+  out[(size_t)t * ldo + c] = from_f32<TO>(up > 0 ? v * x[(size_t)t * ld + up + c] : v);
 }
 
 // Four neighbouring values a thread (rows that can be read and written in whole pieces of four); the same
 // arithmetic per value as above.
 template <typename TO>
-__global__ void act_rows4_kernel(const float* x, long long ld, TO* out, long long ldo, int n, int inner4, int kind) {
+__global__ void act_rows4_kernel(const float* x, long long ld, TO* out, long long ldo, int n, int inner4, int kind,
+                                 int up) {
   pdl_trigger();
   pdl_wait();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long long)n * inner4) return;
   const int t = (int)(i / inner4), c = 4 * (int)(i - (long long)t * inner4);
   const float4 v = *reinterpret_cast<const float4*>(x + (size_t)t * ld + c);
-  const float r0 = act_value(v.x, kind), r1 = act_value(v.y, kind), r2 = act_value(v.z, kind), r3 = act_value(v.w, kind);
+  float r0 = act_value(v.x, kind), r1 = act_value(v.y, kind), r2 = act_value(v.z, kind), r3 = act_value(v.w, kind);
+  if (up > 0) {
+    const float4 u = *reinterpret_cast<const float4*>(x + (size_t)t * ld + up + c);
+    r0 *= u.x; r1 *= u.y; r2 *= u.z; r3 *= u.w;
+  }
   TO* o = out + (size_t)t * ldo + c;
   if constexpr (sizeof(TO) == 2) {
     __nv_bfloat162 lo = __floats2bfloat162_rn(r0, r1), hi = __floats2bfloat162_rn(r2, r3);
@@ -511,10 +577,27 @@ GB_OP(gb_op_gated_group_norm) {
   return 1;
 }
 
+// a0 x (f32, the stream), a1 its row stride, a2 y1 (f32), a3 its row stride, a4 s1 [dim] (f32), a5 y2 (f32) or 0, a6 its
+// row stride, a7 s2 [dim] (f32), a8 rows, a9 dim; optionally the norm in front of the next layer, taken of the new rows:
+// a10 its gain (0: none), a11 out [rows, dim], a12 out dtype, a13 kind; f0 the factor on the sum, f1 that norm's eps
+GB_OP(gb_op_scaled_sum) {
+  const int n = (int)a[8], dim = (int)a[9];
+  if (n <= 0) return 0;
+  if (a[5] && !a[7]) GB_FAIL(GB_ERR_ARG, "scaled_sum: a second branch without its scale");
+  ThenNorm then{op_ptr<const float>(a[10]), op_ptr<void>(a[11]), (int)a[12], (int)a[13], (float)f[1]};
+  const dim3 block(dim >= 2048 ? 512 : dim > 512 ? 256 : 128);
+  gb_launch(scaled_sum_kernel, dim3(n), block, 0, ctx->stream, op_ptr<float>(a[0]), a[1], op_ptr<const float>(a[2]), a[3],
+            op_ptr<const float>(a[4]), op_ptr<const float>(a[5]), a[6], op_ptr<const float>(a[7]), dim, (float)f[0], then);
+  GB_CHECK_LAUNCH("scaled_sum");
+  return 1;
+}
+
 // a0 x (f32), a1 its row stride, a2 out [rows, inner], a3 out dtype, a4 its row stride, a5 rows, a6 inner, a7 which
-// function: 0 gelu (erf), 1 gelu (tanh), 2 silu, 3 relu
+// function: 0 gelu (erf), 1 gelu (tanh), 2 silu, 3 relu, a8 gated (0/1): the rows are [g | u] of `inner` entries each
+// and out = act(g) * u
 GB_OP(gb_op_act_rows) {
   const int n = (int)a[5], inner = (int)a[6];
+  const int up = a[8] ? inner : 0;
   if (n <= 0) return 0;
   if (a[7] > ACT_RELU) GB_FAIL(GB_ERR_ARG, "act_rows: function %lld", a[7]);
   const size_t out_bytes = a[3] == GB_BF16 ? 2 : 4;
@@ -522,20 +605,20 @@ GB_OP(gb_op_act_rows) {
     const dim3 grid4(gb_div_up((long long)n * (inner / 4), 256)), block4(256);
     if (a[3] == GB_BF16)
       gb_launch(act_rows4_kernel<bf16>, grid4, block4, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], op_ptr<bf16>(a[2]),
-                a[4], n, inner / 4, (int)a[7]);
+                a[4], n, inner / 4, (int)a[7], up);
     else
       gb_launch(act_rows4_kernel<float>, grid4, block4, 0, ctx->stream, op_ptr<const float>(a[0]), a[1],
-                op_ptr<float>(a[2]), a[4], n, inner / 4, (int)a[7]);
+                op_ptr<float>(a[2]), a[4], n, inner / 4, (int)a[7], up);
     GB_CHECK_LAUNCH("act_rows (four a thread)");
     return 1;
   }
   const dim3 grid(gb_div_up((long long)n * inner, 256)), block(256);
   if (a[3] == GB_BF16)
     gb_launch(act_rows_kernel<bf16>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], op_ptr<bf16>(a[2]), a[4],
-              n, inner, (int)a[7]);
+              n, inner, (int)a[7], up);
   else
     gb_launch(act_rows_kernel<float>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], op_ptr<float>(a[2]),
-              a[4], n, inner, (int)a[7]);
+              a[4], n, inner, (int)a[7], up);
   GB_CHECK_LAUNCH("act_rows");
   return 1;
 }

@@ -93,13 +93,14 @@ enum NormFlag : int { NF_LAZY = 1 };      // the product after it may run the no
 constexpr int FIRST_REGISTERED_OP = 64;
 constexpr int MAX_REGISTERED_OPS = 64;
 
-struct PlanOp {              // 224 bytes; the meaning of a[] per operation is given where it is executed
+struct PlanOp {              // 232 bytes; the meaning of a[] per operation is given where it is executed
   int op;
   int flags;
   long long a[24];
   double f[3];
+  long long label;           // which entry of the timing table the record's time is added to
 };
-static_assert(sizeof(PlanOp) == 224, "operation size");
+static_assert(sizeof(PlanOp) == 232, "operation size");
 
 struct Walk {
   const long long* sym;
@@ -464,7 +465,7 @@ struct GbPlanRun {
   float* ssq; int decode_products;
   float* residual; long long residual_ld;
   // timing != 0: every operation is bracketed by CUDA events (which also keeps operations from
-  // overlapping) and its time is added to label_ms[a[23]] of its record; for measurements only
+  // overlapping) and its time is added to label_ms[label] of its record; for measurements only
   int timing; int n_labels;
   float* label_ms; int* label_count;
 };
@@ -501,7 +502,7 @@ GB_API int gb_plan_run(GbPlanRun* r, cudaStream_t stream) {
   if (r->timing) {
     GB_CUDA(cudaStreamSynchronize(stream));
     for (int i = 0; i < r->n_ops; ++i) {
-      const long long label = ops[i].a[23];
+      const long long label = ops[i].label;
       float ms = 0.f;
       if (label >= 0 && label < r->n_labels && cudaEventElapsedTime(&ms, events[2 * i], events[2 * i + 1]) == cudaSuccess) {
         r->label_ms[label] += ms;

@@ -27,7 +27,7 @@ from .. import ops
 from ..ops.library import KernelError, library
 from ..parts.base import NotPlannable
 
-OP = np.dtype([("op", "<i4"), ("flags", "<i4"), ("a", "<i8", (24,)), ("f", "<f8", (3,))])
+OP = np.dtype([("op", "<i4"), ("flags", "<i4"), ("a", "<i8", (24,)), ("f", "<f8", (3,)), ("label", "<i8")])
 
 P_EMBED, P_RMSNORM, P_LINEAR, P_SHORT_CONV, P_QKROPE, P_ATTENTION, P_SWIGLU, P_SCALE_SOFTCAP = range(1, 9)
 LF_RESIDUAL, LF_PARTIALS_IF_ONE_EACH, LF_PARTIALS, LF_NORMED = 1, 2, 4, 8
@@ -132,10 +132,10 @@ class PlanBuilder:
 
     def emit(self, op: int, a, f=(), flags: int = 0, label: str = "") -> None:
         """Append one record: a built-in operation (P_...) or the id ``register_op`` gave.
-        ``label``: the name its time is added up under in timing mode (operand 23 is kept for it)."""
+        ``label``: the name its time is added up under in timing mode."""
         self._lazy = None
-        if len(a) > 23:
-            raise NotPlannable("an operation has 23 integer operands")
+        if len(a) > 24 or len(f) > 3:
+            raise NotPlannable("an operation has 24 integer and 3 floating-point operands")
         if any(int(v) < 0 for v in a):
             # (bit 62 marks a symbol, and every negative number has it set)
             raise ValueError(f"operation {label or op}: operands are non-negative numbers, addresses or symbols; got {list(a)}")
@@ -145,7 +145,7 @@ class PlanBuilder:
         rec = np.zeros((), dtype=OP)
         rec["op"], rec["flags"] = op, flags
         rec["a"][:len(a)] = a
-        rec["a"][23] = self.labels.index(label)
+        rec["label"] = self.labels.index(label)
         rec["f"][:len(f)] = f
         self.ops.append(rec)
 

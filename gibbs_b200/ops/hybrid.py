@@ -23,7 +23,7 @@ OPERATIONS = ("row_norm", "norm_add", "clamped_glu", "gelu_mul_rows", "gated_gro
               "ssm_scan", "latent_prep", "head_linear", "latent_attention", "moe_route", "moe_sort", "moe_gather",
               "moe_experts", "moe_experts_tc", "moe_combine", "moe_route_grouped", "moe_combine_weighted",
               "embed_scaled", "qk_prep", "sink_attention", "sink_attention_tc", "act_rows", "head_norm", "delta_prep",
-              "delta_scan")
+              "delta_scan", "scaled_sum")
 
 NORM_LAYER, NORM_RMS = 0, 1
 TAKES_PENDING = 1 << 30          # a record's flag: the operation adds the sums a product left pending itself

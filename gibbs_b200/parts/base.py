@@ -25,6 +25,9 @@ Categories and what each must implement:
   feed_forward ``forward(h, residual, step)``, adding likewise.
   token_input ``forward(x, step)``: adds to the stream something that depends on the
               tokens' ids as well (a per-layer table looked up by token).
+  branch_sum  ``add(runner, x, branches)``: the residual sum itself, for an arrangement whose
+              sublayers write their outputs and whose sum has weights of its own (a scale per
+              channel and sublayer, a factor on the whole).
   A mixer or feed-forward with ``writes_branch`` (``parts.runner.BranchPart``) can also
   WRITE its output into a float32 tensor given in place of the stream, for arrangements
   that put a norm between the sublayer and the residual sum.
@@ -79,10 +82,14 @@ class PagedKV:
     # positions are seen in blocks of this many, counted from 0: a position needs the keys of its own block
     # only, so the pages of earlier blocks go back as soon as a request has moved on (not together with ``window``)
     block: Optional[int] = None
+    # with a window: the pages that hold the first ``keep_first`` positions of a sequence stay as well
+    keep_first: int = 0
 
     def __post_init__(self):
         if self.window is not None and self.block is not None:
             raise ValueError("pages are kept for a window or for a block of positions, not both")
+        if self.keep_first and self.window is None:
+            raise ValueError("first positions are kept beside a window")
 
     @property
     def value_dim(self) -> int:
@@ -90,8 +97,11 @@ class PagedKV:
 
     @property
     def retention(self):
-        """What groups caches into pools: None (every position), a window length, or ("block", size)."""
-        return ("block", self.block) if self.block is not None else self.window
+        """What groups caches into pools: None (every position), a window length, ("block", size), or
+        ("window", length, kept first positions)."""
+        if self.block is not None:
+            return ("block", self.block)
+        return ("window", self.window, self.keep_first) if self.keep_first else self.window
 
 
 @dataclass(frozen=True)
@@ -340,7 +350,7 @@ class Block:
 
 # ---------------------------------------------------------------------------
 _REGISTRY: dict[tuple[str, str], Any] = {}
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "token_input", "block", "embedding", "head")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "token_input", "branch_sum", "block", "embedding", "head")
 
 
 def register_part(category: str, kind: str, cls) -> None:

@@ -3,7 +3,8 @@ from __future__ import annotations
 
 import torch
 
-from .base import Block, plan_ops_of, register_part
+from .. import ops
+from .base import Block, Part, TensorDecl, VECTOR, plan_ops_of, register_part
 from .norm import RowNorm
 from .runner import Eager, Planned, stream_tensor
 
@@ -99,3 +100,88 @@ class SandwichResidual(Block):
 
 
 register_part("block", "sandwich_residual", SandwichResidual)
+
+
+class ScaledSum(Part):
+    """The residual sum of sublayers that run side by side: x += mult * (s_1 * y_1 + s_2 * y_2 + ...), with one
+    scale vector per sublayer (tensors named after the sublayers' roles, ``branches``) and one factor ``mult``
+    on the whole; 32-bit throughout.  One kernel reads the stream and the outputs once."""
+    category = "branch_sum"
+
+    @classmethod
+    def declare(cls, params):
+        return {name: TensorDecl.of(params["dim"], role=VECTOR) for name in params["branches"]}
+
+    def __init__(self, params, tensors, rt):
+        super().__init__(params, tensors, rt)
+        self.dim, self.mult = int(params["dim"]), float(params.get("mult", 1.0))
+        self.branches = tuple(params["branches"])
+        if not 1 <= len(self.branches) <= 2:
+            raise ValueError(f"a sum of {len(self.branches)} sublayers; the kernel takes one or two")
+        self.scales = [tensors[name].to(torch.float32).contiguous() for name in self.branches]
+
+    def kernel_libraries(self):
+        from ..ops import hybrid
+        return ("core", hybrid.LIBRARY)
+
+    def add(self, rn, x: torch.Tensor, outputs: list, then=None):
+        """``outputs``: the sublayers' outputs (float32 [rows, dim]) in the order of ``branches``.  ``then`` (a
+        RowNorm: the norm in front of the next layer) is taken of the new rows in the same kernel; its output is
+        returned."""
+        from .runner import keep
+        if len(outputs) != len(self.branches):
+            raise ValueError(f"{len(outputs)} outputs for the sublayers {self.branches}")
+        y2 = outputs[1] if len(outputs) > 1 else None
+        a = [x.data_ptr(), x.stride(0), outputs[0].data_ptr(), outputs[0].stride(0), keep(rn, self.scales[0]),
+             0 if y2 is None else y2.data_ptr(), 0 if y2 is None else y2.stride(0),
+             0 if y2 is None else keep(rn, self.scales[1]), rn.N, self.dim]
+        f, out = [self.mult], None
+        if then is not None:
+            out = rn.buffer("normed", then.dim)
+            a += [keep(rn, then.gain), out.data_ptr(), ops.dtype_code(out.dtype), then.KIND]
+            f += [then.eps]
+        rn.op("scaled_sum", a, f, label="scaled_sum")
+        return out
+
+
+register_part("branch_sum", "scaled_sum", ScaledSum)
+
+
+class ParallelResidual(Block):
+    """One norm, and both sublayers read its output:
+
+        h = norm(x);  x += sum(mixer(h), ffn(h))
+
+    where ``sum`` is a ``branch_sum`` part (scales per channel, a factor).  The feed-forward is optional.  The
+    sublayers write their outputs (``parts.runner.BranchPart``, or any part with such a ``run``)."""
+    ROLES = (("norm", "norm"), ("mixer", "mixer"), ("ffn", "feed_forward"), ("sum", "branch_sum"))
+    OPTIONAL_ROLES = ("ffn",)
+
+    def __init__(self, parts, rt, params=None):
+        super().__init__(parts, rt, params)
+        for role in ("mixer", "ffn"):
+            if role in self.parts and not getattr(self.parts[role], "writes_branch", False):
+                raise ValueError(f"the {role} of this arrangement must be able to write its output for the sum behind "
+                                 f"it; {type(self.parts[role]).__name__} only adds into the stream")
+        want = ("mixer", "ffn") if "ffn" in self.parts else ("mixer",)
+        if tuple(self.parts["sum"].branches) != want:
+            raise ValueError(f"the sum is over {self.parts['sum'].branches}; the layer has {want}")
+
+    def _run(self, rn, x, caches, h):
+        hidden = x.shape[1]
+        outputs = [rn.buffer("branch", hidden, torch.float32)]
+        self.mixer.run(rn, h, outputs[0], self.caches_of("mixer", caches))
+        if "ffn" in self.parts:
+            outputs.append(rn.buffer("branch_ffn", hidden, torch.float32))
+            self.ffn.run(rn, h, outputs[1], None)
+        self.sum.add(rn, x, outputs)
+
+    def forward(self, x, step, caches):
+        xt = stream_tensor(x)
+        self._run(Eager(self.rt, step), xt, caches, self.norm.forward(xt))
+
+    def plan_ops(self, plan, caches):
+        self._run(Planned(plan), plan.residual, caches, plan_ops_of(self.norm)(plan))
+
+
+register_part("block", "parallel_residual", ParallelResidual)

@@ -15,7 +15,11 @@ the device (no host round trip), the experts' products run over the ragged row
 ranges (csrc/moe.cu).
 
 The router's rule is made of parameters, so that other designs can set it:
-``scores`` "sigmoid" (default) or "softmax" (over all router outputs);
+``scores`` "sigmoid" (default), "softmax" (over all router outputs) or "logits"
+(the router's outputs as they are); ``normalise`` None (a chosen output's weight
+is its score), "sum" (divided by the sum of the chosen scores) or "softmax" (the
+softmax over the chosen scores alone); ``router_bias``: the logits are
+W_router h + b (tensor ``router.b``);
 ``correction``: a vector added to the scores for the CHOICE only (the weights
 use the scores without it); ``groups`` / ``groups_keep``: the router outputs
 form that many equal groups of neighbours, a group's mark is its largest choice
@@ -81,6 +85,8 @@ class RoutedGLU(BranchPart, FeedForward):
     def declare(cls, params):
         h, E, f = params["hidden"], params["experts"], params["expert_inner"]
         d = {"router": TensorDecl.of(E + int(params.get("identity", 0) or 0), h)}
+        if params.get("router_bias"):
+            d["router.b"] = TensorDecl.of(E + int(params.get("identity", 0) or 0), role=VECTOR)
         if params.get("correction"):
             d["correction"] = TensorDecl.of(E + int(params.get("identity", 0) or 0), role=VECTOR)
         for e in range(E):
@@ -99,7 +105,8 @@ class RoutedGLU(BranchPart, FeedForward):
         self.alpha, self.up_add = float(p.get("alpha", 1.702)), float(p.get("up_add", 1.0))
         self.identity = int(p.get("identity", 0) or 0)
         self.n_out = self.E + self.identity                      # router outputs
-        self.scores = {"sigmoid": 0, "softmax": 1}[p.get("scores", "sigmoid")]
+        self.scores = {"sigmoid": 0, "softmax": 1, "logits": 2}[p.get("scores", "sigmoid")]
+        self.normalise = {None: 0, "sum": 1, "softmax": 2}[p.get("normalise")]
         self.groups = int(p.get("groups", 1) or 1)
         self.groups_keep = int(p.get("groups_keep", self.groups) or self.groups)
         self.weight_on_output = {"input": False, "output": True}[p.get("weight_on", "input")]
@@ -111,7 +118,8 @@ class RoutedGLU(BranchPart, FeedForward):
         if self.identity and not self.weight_on_output:
             raise ValueError("identity experts come with weights on the experts' outputs")
         # the plain rule (sigmoid scores, the largest win) has a kernel of its own
-        self.plain_rule = (self.scores == 0 and self.correction is None and self.groups == 1 and not self.identity)
+        self.plain_rule = (self.scores == 0 and self.correction is None and self.groups == 1 and not self.identity
+                           and not self.normalise)
         self.adds_in_place = self.weight_on_output
         E = self.E
         # gate and up rows of an expert side by side; in blocks of 64 features where the width allows, the
@@ -131,6 +139,11 @@ class RoutedGLU(BranchPart, FeedForward):
             rows.append(tensors["shared.sg"].reshape(1, self.hidden))
         # the router and the shared expert's gate in one small 32-bit product
         self.w_router = torch.cat(rows, 0).contiguous()
+        self.router_bias = None
+        if p.get("router_bias"):
+            if p.get("shared_inner"):
+                raise ValueError("a router with a bias has no shared expert's gate beside it")
+            self.router_bias = tensors["router.b"].to(torch.float32).contiguous()
 
     def kernel_libraries(self):
         return tuple(set(ops.linear_libraries(self.w_down.dtype, self.rt.dtype)) | {"core", hybrid.LIBRARY})
@@ -151,7 +164,7 @@ class RoutedGLU(BranchPart, FeedForward):
         if accumulate and not self.weight_on_output:
             raise ValueError("a routed unit with weights on the experts' inputs writes its output")
         logits = rn.buffer("moe_logits", n_out + (1 if shared else 0), torch.float32)
-        rn.linear(h, self.w_router, None, logits, role="router")
+        rn.linear(h, self.w_router, self.router_bias, logits, role="router")
         idx = rn.buffer("moe_choice", top, torch.int32)
         wts = rn.buffer("moe_weight", top, torch.float32)
         sg = rn.buffer("moe_shared_gate", 1, torch.float32)
@@ -163,7 +176,7 @@ class RoutedGLU(BranchPart, FeedForward):
                 raise ValueError("a shared expert's gate comes with the plain router rule")
             rn.op("moe_route_grouped", [logits.data_ptr(), logits.stride(0), rn.N, n_out, top, self.scores,
                                         keep(rn, self.correction), self.groups, self.groups_keep, idx.data_ptr(),
-                                        wts.data_ptr()])
+                                        wts.data_ptr(), self.normalise])
         # (identity outputs are sorted behind the experts: their rows lie beyond offsets[E] and no product reads them)
         offsets = rn.buffer("moe_offsets", n_out + 1, torch.int32, fixed_rows=1)
         row_pair = rn.buffer("moe_row_pair", top, torch.int32)

@@ -1,9 +1,11 @@
-"""A feed-forward without a gate: out = W_down act(W_up h).
+"""Feed-forwards whose activation is named: without a gate, out = W_down act(W_up h)
+(``dense_mlp``), and with one, out = W_down (act(W_gate h) * (W_up h)) (``gated_mlp``).
 
 ``act`` is one of "gelu" (the exact one, with erf), "gelu_tanh", "silu",
-"relu".  The first product writes 32-bit values, the function is taken in
-32-bit and rounded to the compute dtype for the second product, which adds
-into the residual stream.
+"relu".  The first product writes 32-bit values, the function (and the gate's
+product with the up rows) is taken in 32-bit and rounded to the compute dtype
+for the second product, which adds into the residual stream or writes for an
+arrangement that takes the output as it is.
 """
 from __future__ import annotations
 
@@ -51,4 +53,38 @@ class DenseMLP(BranchPart, FeedForward):
         (rn.add_linear if accumulate else rn.linear)(act, self.down, self.down_bias, out, role="mlp_down")
 
 
+class GatedMLP(BranchPart, FeedForward):
+    adds_in_place = True
+
+    @classmethod
+    def declare(cls, params):
+        h, f = params["hidden"], params["inner"]
+        return {"gate": TensorDecl.of(f, h), "up": TensorDecl.of(f, h), "down": TensorDecl.of(h, f)}
+
+    def __init__(self, params, tensors, rt):
+        super().__init__(params, tensors, rt)
+        self.hidden, self.inner = int(params["hidden"]), int(params["inner"])
+        act = params.get("act", "silu")
+        if act not in ACTIVATIONS:
+            raise ValueError(f"unknown activation '{act}'; known: {sorted(ACTIVATIONS)}")
+        self.act = ACTIVATIONS[act]
+        if tensors["gate"].dtype != tensors["up"].dtype:
+            raise ValueError("gate and up projections are stored in different dtypes")
+        # one product for [gate rows | up rows]
+        self.gate_up = torch.cat([tensors["gate"], tensors["up"]], 0).contiguous()
+        self.down = tensors["down"].contiguous()
+
+    def kernel_libraries(self):
+        return tuple(set(ops.linear_libraries(self.gate_up.dtype, self.rt.dtype)) | {"core", hybrid.LIBRARY})
+
+    def run(self, rn: Runner, h, out, caches=None, accumulate: bool = False):
+        gu = rn.buffer("gmlp_gate_up", 2 * self.inner, torch.float32)
+        rn.linear(h, self.gate_up, None, gu, role="mlp_gate_up")
+        act = rn.buffer("gmlp_act", self.inner)
+        rn.op("act_rows", [gu.data_ptr(), gu.stride(0), act.data_ptr(), ops.dtype_code(act.dtype), act.stride(0), rn.N,
+                           self.inner, self.act, 1], label="act_rows:gated")
+        (rn.add_linear if accumulate else rn.linear)(act, self.down, None, out, role="mlp_down")
+
+
 register_part("feed_forward", "dense_mlp", DenseMLP)
+register_part("feed_forward", "gated_mlp", GatedMLP)

@@ -4,7 +4,11 @@ RMSNorm: x * (1/sqrt(mean(x^2) + eps)) * gain, statistics in 32-bit
 (MisterTK/gibbs arch/lib/transformer.json5:9-11; src/model/simd.rs:73-111), with the
 split-K and decode-product couplings of the core kernels.  RowNorm and its kinds (layer
 norm, plain RMS norm): the same statistics on the hybrid library, usable in front of a
-sublayer and behind one."""
+sublayer and behind one.
+
+``gain_offset`` (every kind; default 0): the stored weight is the gain's distance from this number, so a
+design that keeps its norm weights around zero sets 1 and the rows are multiplied by 1 + weight.  The sum is
+taken once, in 32-bit, when the part is built."""
 from __future__ import annotations
 
 import torch
@@ -15,6 +19,13 @@ from .base import Norm, Residual, TensorDecl, VECTOR, register_part
 from .runner import Planned, Runner, keep, stream_tensor
 
 
+def stored_gain(weight: torch.Tensor, params: dict) -> torch.Tensor:
+    """The 32-bit gain a norm multiplies by: the stored weight plus ``gain_offset``."""
+    gain = weight.to(torch.float32)
+    offset = float(params.get("gain_offset", 0.0) or 0.0)
+    return (gain + offset if offset else gain).contiguous()
+
+
 class RMSNorm(Norm):
     @classmethod
     def declare(cls, params):
@@ -23,7 +34,7 @@ class RMSNorm(Norm):
     def __init__(self, params, tensors, rt):
         super().__init__(params, tensors, rt)
         self.dim, self.eps = int(params["dim"]), float(params["eps"])
-        self.gain = tensors["weight"].to(torch.float32).contiguous()
+        self.gain = stored_gain(tensors["weight"], params)
 
     def forward(self, x, out=None, rows=None):
         pending = None
@@ -66,7 +77,7 @@ class RowNorm(Norm):
     def __init__(self, params, tensors, rt):
         super().__init__(params, tensors, rt)
         self.dim, self.eps = int(params["dim"]), float(params["eps"])
-        self.gain = tensors["weight"].to(torch.float32).contiguous()
+        self.gain = stored_gain(tensors["weight"], params)
 
     def kernel_libraries(self):
         return ("core", hybrid.LIBRARY)

@@ -1,6 +1,7 @@
 """Random weights from a configuration and a seed: matrices, tables and biases
 N(0, 0.02), norm gains 1.0 (optionally jittered, so that tests can tell a gain
-from no gain).  Each tensor has its own generator seeded by (seed, name), so a
+from no gain), and the values a plan names for vectors of another kind
+(``ModelPlan.random_values``).  Each tensor has its own generator seeded by (seed, name), so a
 tensor's values do not depend on which other tensors exist.
 
 MisterTK/gibbs has random weights only for synthetic llama ids
@@ -9,6 +10,7 @@ project's benchmark configurations name.
 """
 from __future__ import annotations
 
+import fnmatch
 import hashlib
 import json
 from pathlib import Path
@@ -39,8 +41,9 @@ def random_tensors(plan: ModelPlan, seed: int, dtype: torch.dtype = torch.float3
     for name, decl in expected_tensors(plan).items():
         shape = decl.shapes[-1]            # the shape checkpoints of this architecture use
         g = torch.Generator().manual_seed(_seed_for(seed, name))
-        if decl.role == VECTOR and _is_gain(name):
-            t = torch.ones(shape)
+        fixed = next((v for pat, v in getattr(plan, "random_values", ()) if fnmatch.fnmatchcase(name, pat)), None)
+        if decl.role == VECTOR and (fixed is not None or _is_gain(name)):
+            t = torch.full(shape, 1.0 if fixed is None else float(fixed))
             if gain_jitter:
                 t = t + gain_jitter * torch.randn(shape, generator=g)
         else:
