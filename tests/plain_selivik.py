@@ -161,6 +161,9 @@ def experts(h, W, p, f):
     return out
 
 
+MIXERS = {"latent_attention": latent_attention, "attention": attention}
+
+
 def forward(cfg, W, tokens, streams=False):
     """Logits [T, vocab] of one sequence; with ``streams`` also the residual stream behind every layer."""
     W = {k: v.to(F64) for k, v in W.items()}
@@ -170,8 +173,7 @@ def forward(cfg, W, tokens, streams=False):
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
         h = norm_around_zero(x, W[p + "norm1"], eps)
-        mix = {"latent_attention": latent_attention, "attention": attention}[layer["type"]]
-        y = mix(h, W, p + "mix.", layer["mixer"], eps) * W[p + "ls1"]
+        y = MIXERS[layer["type"]](h, W, p + "mix.", layer["mixer"], eps) * W[p + "ls1"]
         f = layer.get("mlp")
         if f is not None:
             ff = dense_unit(h, W, p + "mlp.") if f["kind"] == "dense" else experts(h, W, p + "mlp.", f)

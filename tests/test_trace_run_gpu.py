@@ -211,3 +211,35 @@ def test_trace_run_sisadra_from_a_folder_without_rank_keys(tmp_path, dtype):
         if rows:
             e = rel_rows(np.stack([got[rid][p] for p in rows]), want[rid][rows])
             assert e.max() <= (2e-4 if dtype == "float32" else 4e-2), f"{rid}: place {rows[int(e.argmax())]} differs by {e.max():.3g}"
+
+
+def test_trace_run_selivik(tmp_path):
+    """The Selivik design through the same runner: a model folder on disk (bfloat16 weights), both compute
+    dtypes, mixed steps with sparse wants in a pool that makes pages go round (windows with kept first
+    positions among them)."""
+    import plain_selivik
+    from potivik_helpers import rel_rows, write_model
+    from selivik_helpers import CFG_D, make_weights
+    W = make_weights(CFG_D, 23)
+    folder = write_model(tmp_path / "selivik_d", CFG_D, W)
+    vocab = CFG_D["vocab"]
+    reqs = {f"q{i}": random_ids(90 + i, n, vocab) for i, n in enumerate([70, 45, 130, 1, 64, 20])}
+    steps = trace_mixed(reqs, capacity_tokens=320, max_live=4, seed=6)
+    for k, s in enumerate(steps):
+        for e in s["entries"]:
+            e["want"] = [] if k % 5 == 4 else [w for w in e["want"] if (w + k) % 3]
+    want = {rid: plain_selivik.forward(CFG_D, W, ids).numpy() for rid, ids in reqs.items()}
+    for dtype, tol in (("float32", 2e-4), ("bfloat16", 4e-2)):
+        out = tmp_path / f"out_{dtype}"
+        _run(folder, dtype, steps, out, max_tokens=320)
+        got = _collect(steps, out, vocab)
+        errs = []
+        for rid in reqs:
+            rows = sorted(got.get(rid, {}))
+            if rows:
+                errs.append(rel_rows(np.stack([got[rid][p] for p in rows]), want[rid][rows]))
+        errs = np.concatenate(errs)
+        if dtype == "float32":
+            assert errs.max() <= tol, f"a place differs by {errs.max():.3g}"
+        else:                        # (a router's choice at a near tie may flip under bfloat16 rounding)
+            assert np.median(errs) <= tol and (errs <= tol).mean() >= 0.9
