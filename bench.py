@@ -113,6 +113,31 @@ def sisadra_shape(size: str) -> dict:
             "layers": [{"type": k, "mixer": mixers[k], "mlp": mlp} for k in kinds]}
 
 
+def selivik_shape(size: str) -> dict:
+    """Layer sizes that resemble a real model's, for the Selivik design: latent-attention layers in turn with
+    windowed attention layers that keep a sequence's first positions; a dense gated unit behind the first layer
+    of every four, routed experts behind the others."""
+    if size == "1k":
+        d, vocab = 1024, 32768
+        att = {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 64, "scale": 0.125, "softcap": 30.0,
+               "mask": {"size": 512, "keep_first": 64}, "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0}}}
+        lat = {"heads": 8, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 256, "q_rank": 384, "scale": 96 ** -0.5,
+               "rot": {"base": 10000.0, "dims": 32}}
+        dense = {"kind": "dense", "ff": 4096}
+        moe = {"kind": "moe", "router": {"experts": 16, "top": 2}, "expert": {"ff": 1024}}
+    else:
+        d, vocab = 2048, 65536
+        att = {"heads": 32, "kv_heads": 8, "dim": 64, "vdim": 64, "scale": 0.125, "softcap": 30.0,
+               "mask": {"size": 1024, "keep_first": 128}, "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0}}}
+        lat = {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": 768, "scale": 192 ** -0.5,
+               "rot": {"base": 10000.0, "dims": 64}}
+        dense = {"kind": "dense", "ff": 8192}
+        moe = {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": 1024}}
+    four = [("latent_attention", lat, dense), ("attention", att, moe), ("latent_attention", lat, moe), ("attention", att, moe)]
+    return {"architecture": "Selivik", "vocab": vocab, "width": d, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "embedding": {"scale": 8.0}, "layers": [{"type": k, "mixer": m, "mlp": f} for k, m, f in four * 2]}
+
+
 def potivik_workload(a):
     """Prompt and decode throughput of the Potivik design at two sizes (random weights), beside an LFM2
     model of equal width, depth and feed-forward width, with the time per kind of operation of one
@@ -120,7 +145,9 @@ def potivik_workload(a):
     'petelix': the same for the Petelix design, beside an LFM2 model whose layers are all attention layers
     and whose feed-forward is as wide as the experts a token uses.  'sisadra': the same for the Sisadra design,
     beside an LFM2 model and a Potivik model (state-space and latent-attention layers in turn) of equal width,
-    depth and feed-forward width."""
+    depth and feed-forward width.  'selivik': the Selivik design beside an LFM2 model, a Petelix model (windowed
+    attention with a sink and routed experts) and a Potivik model (latent attention with a rotated part) of equal
+    width and depth."""
     import torch
     from gibbs_b200 import Engine, Lfm2Config, parse_config, random_model
     from gibbs_b200.engine import benchmark as B
@@ -139,6 +166,12 @@ def potivik_workload(a):
             twin = dict(LFM2_1P2B, hidden_size=d, num_hidden_layers=8, num_attention_heads=d // 64, num_key_value_heads=d // 256,
                         head_dim=64, vocab_size=pot["vocab"], intermediate_size=4 * d, block_auto_adjust_ff_dim=False,
                         full_attn_idxs=[1, 3, 5, 7], max_position_embeddings=4096)
+        elif a.workload == "selivik":
+            pot = selivik_shape(size)
+            d = pot["width"]
+            twin = dict(LFM2_1P2B, hidden_size=d, num_hidden_layers=8, num_attention_heads=d // 64, num_key_value_heads=d // 256,
+                        head_dim=64, vocab_size=pot["vocab"], intermediate_size=4 * d, block_auto_adjust_ff_dim=False,
+                        full_attn_idxs=[1, 3, 5, 7], max_position_embeddings=4096)
         else:
             pot = potivik_shape(size)
             d = pot["width"]
@@ -147,6 +180,9 @@ def potivik_workload(a):
                         full_attn_idxs=[1, 3, 5, 7], max_position_embeddings=4096)
         models = [(pot["architecture"], parse_config(pot)), ("LFM2 of equal size", Lfm2Config.from_dict(twin))]
         if a.workload == "sisadra":
+            models.append(("Potivik of equal size", parse_config(potivik_shape(size))))
+        if a.workload == "selivik":
+            models.append(("Petelix of equal size", parse_config(petelix_shape(size))))
             models.append(("Potivik of equal size", parse_config(potivik_shape(size))))
         for name, conf in models:
             model = random_model(conf, SEED, dtype="bfloat16", device="cuda:0", stored_dtype=torch.bfloat16)
@@ -239,10 +275,10 @@ def main():
                     help="float32: the engine's true 32-bit twin on the same (bfloat16-rounded) weights; "
                          "with --only prefill or --only decode (the benchmark line itself is bfloat16)")
     ap.add_argument("--skip-points", action="store_true", help="skip batch 1 and 64")
-    ap.add_argument("--workload", choices=["serve700m", "long2p6b", "sweep", "potivik", "petelix", "sisadra"], default=None,
+    ap.add_argument("--workload", choices=["serve700m", "long2p6b", "sweep", "potivik", "petelix", "sisadra", "selivik"], default=None,
                     help="run one of the other workloads instead (prints its own JSON lines); 'potivik' / 'petelix' / "
-                         "'sisadra': that design at layer sizes of a real model, beside an LFM2 model of equal size")
-    ap.add_argument("--size", default=None, help="with --workload potivik, petelix or sisadra: '1k', '2k' or both with a comma (default both)")
+                         "'sisadra' / 'selivik': that design at layer sizes of a real model, beside an LFM2 model of equal size")
+    ap.add_argument("--size", default=None, help="with --workload potivik, petelix, sisadra or selivik: '1k', '2k' or both with a comma (default both)")
     ap.add_argument("--prompt-tokens", type=int, default=None,
                     help="with --only prefill / prefill-timeline / products: another prompt length than 2,048")
     ap.add_argument("--only", default=None,
@@ -265,7 +301,7 @@ def main():
     from gibbs_b200 import Generator, Lfm2Config, random_model
     from gibbs_b200.engine import benchmark as B
 
-    if a.workload in ("potivik", "petelix", "sisadra"):
+    if a.workload in ("potivik", "petelix", "sisadra", "selivik"):
         return potivik_workload(a)
     if a.workload:
         return other_workload(a)

@@ -398,7 +398,7 @@ bool gb_latent_attention_tc_takes(int n, int R, int H, int r, int dr, int window
 int gb_latent_attention_tc_launch(const float* qp, const bf16* pages, const int* block_table, int bt_stride, int page_size,
                                   int n_pages, const int* tok_req, const int* tok_pos, const int* q_start,
                                   const float* gate, long long ld_gate, float* out, long long ldo, int n, int R, int H, int r,
-                                  float scale, const float* sink, int* status, cudaStream_t stream);
+                                  int dr, float scale, const float* sink, int* status, cudaStream_t stream);
 
 // How the visible keys of a launch are cut into chunks of whole key tiles: (chunks, keys per chunk).
 // Few tokens (decoding) get many chunks, so that the GPU is occupied; a launch with enough (token, head
@@ -498,7 +498,7 @@ GB_OP(gb_op_latent_attention) {
     if (gb_latent_attention_tc_launch(op_ptr<const float>(a[0]), op_ptr<const bf16>(a[1]), op_ptr<const int>(a[3]), (int)a[4],
                                       (int)a[5], (int)a[6], op_ptr<const int>(a[7]), op_ptr<const int>(a[8]),
                                       op_ptr<const int>(a[22]), op_ptr<const float>(a[9]), a[10],
-                                      op_ptr<float>(a[11]), a[12], n, (int)a[21], H, r, (float)f[0],
+                                      op_ptr<float>(a[11]), a[12], n, (int)a[21], H, r, dr, (float)f[0],
                                       op_ptr<const float>(a[20]), ctx->status, ctx->stream) == 0) {
       GB_CHECK_LAUNCH("latent_attention (tensor cores)");
       return 1;

@@ -1,7 +1,8 @@
 // Attention over a latent cache on tensor cores, in the absorbed form, for steps that carry portions of prompts.
 //
-// Every head's keys AND values are the same cached rows c_j (kv_rank entries, bfloat16): with q'_h = W_uk,h^T q_h the
-// score is q'_h . c_j and the head's output is sum_j p_j c_j.  So the rows of a tile are (token, head) pairs of one
+// Every head's keys AND values are the same cached rows [c_j | k_rot,j] (kv_rank + rot_dim entries, bfloat16; the
+// rotated part may be absent): with q'_h = [W_uk,h^T q_h | rot(q_rot,h)] the score is q'_h . [c_j | k_rot,j] and the
+// head's output is sum_j p_j c_j: the first product reads whole rows, the second their first kv_rank entries.  So the rows of a tile are (token, head) pairs of one
 // request, all of which read the same key rows, and one tile of cached rows in shared memory is the second operand of
 // both products: S = Q' C^T (rows of C as they lie) and O += P C (the same rows, transposed on the way to the
 // registers).
@@ -12,8 +13,9 @@
 //  the block table into two buffers.  mma.sync.m16n8k16, bfloat16 operands, 32-bit accumulators; the softmax (base
 //  2, running maximum and sum per row) is 32-bit, and its weights enter the second product as TWO bfloat16 terms
 //  (p = hi + lo), so 16 bits of every weight count.  A learned sink per head joins the denominator at the end; an
-//  optional gate multiplies the result.  Causal, no window, no rotated part: what has those runs on the generic
-//  kernel, as do 32-bit pages and steps of single tokens.
+//  optional gate multiplies the result.  Causal, no window: what has one runs on the generic kernel, as do 32-bit
+//  pages and steps of single tokens.  Rows in shared memory lie `stride` entries apart: the row's length rounded up
+//  to 16, plus 8 (an odd number of 16-byte pieces, so that ldmatrix meets no bank twice).
 #include "hybrid.cuh"
 
 namespace {
@@ -53,8 +55,8 @@ __device__ __forceinline__ void ltc_split(float x, float y, unsigned& hi, unsign
 }
 
 struct LtcParams {
-  const float* qp;          // [tokens][heads][r]
-  const bf16* pages;        // [n_pages][page_size][r]
+  const float* qp;          // [tokens][heads][dk]
+  const bf16* pages;        // [n_pages][page_size][dk]
   const int* block_table;
   int bt_stride, page_size, n_pages;
   const int* tok_req;
@@ -66,6 +68,7 @@ struct LtcParams {
   float* out;
   long long ldo;
   int H, r, tpt;
+  int dk, stride;           // entries of a cached row (r + rotated part); entries between rows in shared memory
   float scale_log2;
   const float* sink;
   int* status;
@@ -73,7 +76,8 @@ struct LtcParams {
 
 template <int RP>
 __global__ void __launch_bounds__(RP > 256 ? 256 : 128, 1) latent_attention_tc_kernel(const LtcParams p) {
-  constexpr int NSPLIT = RP > 256 ? 2 : 1, OC = RP / NSPLIT, STRIDE = RP + 8, THREADS = 128 * NSPLIT;
+  constexpr int NSPLIT = RP > 256 ? 2 : 1, OC = RP / NSPLIT, THREADS = 128 * NSPLIT;
+  const int STRIDE = p.stride, dk = p.dk;
   extern __shared__ __align__(16) unsigned char ltc_smem[];
   bf16* Qs = reinterpret_cast<bf16*>(ltc_smem);           // [64][STRIDE]
   bf16* Cs = Qs + LTC_ROWS * STRIDE;                       // [2][64][STRIDE]
@@ -91,12 +95,12 @@ __global__ void __launch_bounds__(RP > 256 ? 256 : 128, 1) latent_attention_tc_k
   const int pos0 = p.tok_pos[t_first];
   const int kmax = pos0 + ntok - 1;
   const int* table = p.block_table + (size_t)p.tok_req[t_first] * p.bt_stride;
-  // zeros where nothing is copied: rows beyond the live ones, columns r .. RP
+  // zeros where nothing is copied: rows beyond the live ones, columns dk .. stride
   for (int i = threadIdx.x; i < 3 * LTC_ROWS * STRIDE / 8; i += THREADS)
     reinterpret_cast<uint4*>(ltc_smem)[i] = make_uint4(0u, 0u, 0u, 0u);
   __syncthreads();
 
-  const int pieces = r >> 3;                               // 16-byte pieces of a cached row
+  const int pieces = dk >> 3;                              // 16-byte pieces of a cached row
   auto stage = [&](int kt, int b) {
     bf16* dst = Cs + (size_t)b * LTC_KEYS * STRIDE;
     for (int j = warp; j < LTC_KEYS; j += THREADS / 32) {
@@ -106,7 +110,7 @@ __global__ void __launch_bounds__(RP > 256 ? 256 : 128, 1) latent_attention_tc_k
         if (lane == 0) atomicExch(p.status, LTC_BAD_PAGE_READ);
         continue;                                          // (the row keeps what it had: zeros or an older row)
       }
-      const bf16* src = p.pages + ((size_t)page * p.page_size + key % p.page_size) * r;
+      const bf16* src = p.pages + ((size_t)page * p.page_size + key % p.page_size) * dk;
       for (int c = lane; c < pieces; c += 32) gb_cp_async_16(dst + j * STRIDE + 8 * c, src + 8 * c);
     }
     ltc_commit();
@@ -114,12 +118,12 @@ __global__ void __launch_bounds__(RP > 256 ? 256 : 128, 1) latent_attention_tc_k
   pdl_wait();
   stage(0, 0);
   {
-    // this tile's queries: rows_live consecutive rows of r floats, rounded to bfloat16
-    const float* src = p.qp + (size_t)t_first * H * r;
-    const int quads = r >> 2;
+    // this tile's queries: rows_live consecutive rows of dk floats, rounded to bfloat16
+    const float* src = p.qp + (size_t)t_first * H * dk;
+    const int quads = dk >> 2;
     for (int row = warp; row < rows_live; row += THREADS / 32)
       for (int c = lane; c < quads; c += 32) {
-        const float4 v = *reinterpret_cast<const float4*>(src + (size_t)row * r + 4 * c);
+        const float4 v = *reinterpret_cast<const float4*>(src + (size_t)row * dk + 4 * c);
         uint2 w;
         w.x = ltc_pack(v.x, v.y);
         w.y = ltc_pack(v.z, v.w);
@@ -137,7 +141,7 @@ __global__ void __launch_bounds__(RP > 256 ? 256 : 128, 1) latent_attention_tc_k
 #pragma unroll
   for (int j = 0; j < OC / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
   float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
-  const int ksteps = (r + 15) >> 4;                        // k-steps of the first product that hold anything
+  const int ksteps = (dk + 15) >> 4;                       // k-steps of the first product that hold anything
   const int npairs = min(OC / 16, max(0, (r - wn * OC + 15) >> 4));   // pairs of 8 output columns likewise
 
   const int tiles = kmax / LTC_KEYS + 1;
@@ -268,7 +272,7 @@ __global__ void __launch_bounds__(RP > 256 ? 256 : 128, 1) latent_attention_tc_k
 
 template <int RP> int ltc_launch(const LtcParams& p, int tiles, int R, cudaStream_t stream) {
   constexpr int NSPLIT = RP > 256 ? 2 : 1;
-  const size_t smem = sizeof(bf16) * 3 * LTC_ROWS * (RP + 8);
+  const size_t smem = sizeof(bf16) * 3 * LTC_ROWS * (size_t)p.stride;
   static size_t allowed = 48 * 1024;       // raised once per size, before any stream capture replays the launch
   if (smem > allowed) {
     if (cudaFuncSetAttribute(latent_attention_tc_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
@@ -389,11 +393,13 @@ void gb_head_linear_tc_launch(const float* x, long long ldx, long long xh, const
               gate, ld_gate);
 }
 
-// Whether the tensor-core kernel takes a launch: bfloat16 pages whose rows can be copied in 16-byte pieces, no rotated
-// part, no window, at most 64 heads, and a step that carries portions (eight tokens a request on average).
+// Whether the tensor-core kernel takes a launch: bfloat16 pages whose rows can be copied in 16-byte pieces (a latent
+// and a rotated part of multiples of 8 entries, together at most 576, which is what three tiles of 64 rows leave room
+// for in shared memory), no window, at most 64 heads, and a step that carries portions (eight tokens a request on
+// average).
 bool gb_latent_attention_tc_takes(int n, int R, int H, int r, int dr, int window, bool pages_bf16, const void* pages,
                                   const void* qp, const void* out, long long ldo) {
-  return pages_bf16 && dr == 0 && window == 0 && H >= 1 && H <= LTC_ROWS && r % 8 == 0 && r >= 8 && r <= 512 && R >= 1 &&
+  return pages_bf16 && dr >= 0 && dr % 8 == 0 && r + dr <= 576 && window == 0 && H >= 1 && H <= LTC_ROWS && r % 8 == 0 && r >= 8 && r <= 512 && R >= 1 &&
          n >= 8 * R && (long long)n * H >= 256 && ((uintptr_t)pages & 15) == 0 && ((uintptr_t)qp & 15) == 0 &&
          ((uintptr_t)out & 7) == 0 && ldo % 2 == 0;
 }
@@ -402,8 +408,10 @@ bool gb_latent_attention_tc_takes(int n, int R, int H, int r, int dr, int window
 int gb_latent_attention_tc_launch(const float* qp, const bf16* pages, const int* block_table, int bt_stride, int page_size,
                                   int n_pages, const int* tok_req, const int* tok_pos, const int* q_start,
                                   const float* gate, long long ld_gate, float* out, long long ldo, int n, int R, int H, int r,
-                                  float scale, const float* sink, int* status, cudaStream_t stream) {
+                                  int dr, float scale, const float* sink, int* status, cudaStream_t stream) {
   LtcParams p;
+  p.dk = r + dr;
+  p.stride = 16 * ((p.dk + 15) / 16) + 8;
   p.qp = qp; p.pages = pages; p.block_table = block_table; p.bt_stride = bt_stride; p.page_size = page_size;
   p.n_pages = n_pages; p.tok_req = tok_req; p.tok_pos = tok_pos; p.q_start = q_start; p.n = n; p.R = R; p.gate = gate;
   p.ld_gate = ld_gate; p.out = out; p.ldo = ldo; p.H = H; p.r = r; p.tpt = LTC_ROWS / H;

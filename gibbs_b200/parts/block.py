@@ -147,13 +147,19 @@ class ScaledSum(Part):
 register_part("branch_sum", "scaled_sum", ScaledSum)
 
 
+FUSE_NEXT_NORM = True            # (the tests switch it off to compare the two ways)
+
+
 class ParallelResidual(Block):
     """One norm, and both sublayers read its output:
 
         h = norm(x);  x += sum(mixer(h), ffn(h))
 
     where ``sum`` is a ``branch_sum`` part (scales per channel, a factor).  The feed-forward is optional.  The
-    sublayers write their outputs (``parts.runner.BranchPart``, or any part with such a ``run``)."""
+    sublayers write their outputs (``parts.runner.BranchPart``, or any part with such a ``run``).
+
+    When the layer that runs next is of this kind too, its norm is taken in the kernel of this layer's sum, of the
+    new rows while they are in registers (``hands_over``, which the model calls for neighbours in its order)."""
     ROLES = (("norm", "norm"), ("mixer", "mixer"), ("ffn", "feed_forward"), ("sum", "branch_sum"))
     OPTIONAL_ROLES = ("ffn",)
 
@@ -166,6 +172,16 @@ class ParallelResidual(Block):
         want = ("mixer", "ffn") if "ffn" in self.parts else ("mixer",)
         if tuple(self.parts["sum"].branches) != want:
             raise ValueError(f"the sum is over {self.parts['sum'].branches}; the layer has {want}")
+        self._next = None          # the block that runs next, when its norm is taken here
+        self._handed = None        # the normed rows the block in front left for this one
+
+    def hands_over(self, following) -> bool:
+        """Called once when the model is put together: ``following`` runs right behind this block, and only there."""
+        if (FUSE_NEXT_NORM and isinstance(following, ParallelResidual) and isinstance(following.norm, RowNorm)
+                and following.norm.dim == self.sum.dim):
+            self._next = following
+            return True
+        return False
 
     def _run(self, rn, x, caches, h):
         hidden = x.shape[1]
@@ -174,14 +190,23 @@ class ParallelResidual(Block):
         if "ffn" in self.parts:
             outputs.append(rn.buffer("branch_ffn", hidden, torch.float32))
             self.ffn.run(rn, h, outputs[1], None)
-        self.sum.add(rn, x, outputs)
+        if self._next is None:
+            self.sum.add(rn, x, outputs)
+        else:
+            self._next._handed = self.sum.add(rn, x, outputs, then=self._next.norm)
+
+    def _take_handed(self):
+        h, self._handed = self._handed, None
+        return h
 
     def forward(self, x, step, caches):
         xt = stream_tensor(x)
-        self._run(Eager(self.rt, step), xt, caches, self.norm.forward(xt))
+        h = self._take_handed()
+        self._run(Eager(self.rt, step), xt, caches, self.norm.forward(xt) if h is None else h)
 
     def plan_ops(self, plan, caches):
-        self._run(Planned(plan), plan.residual, caches, plan_ops_of(self.norm)(plan))
+        h = self._take_handed()
+        self._run(Planned(plan), plan.residual, caches, plan_ops_of(self.norm)(plan) if h is None else h)
 
 
 register_part("block", "parallel_residual", ParallelResidual)

@@ -26,6 +26,16 @@ class CausalLM:
         self.plan, self.rt = plan, rt
         self.embedding, self.blocks, self.final_norm, self.head = embedding, blocks, final_norm, head
         self.vocab_size, self.hidden_size = plan.vocab_size, plan.hidden_size
+        # neighbours in the order may share a kernel across their border (the norm in front of the next layer taken
+        # by the kernel that completes this one's residual sum): a block that can says so with ``hands_over``.  Only
+        # for layers that run once, so that "the block behind" is one block.
+        runs = {}
+        for e in plan.order:
+            runs[e.layer] = runs.get(e.layer, 0) + 1
+        for a, b in zip(plan.order, plan.order[1:]):
+            hand = getattr(blocks[a.layer], "hands_over", None)
+            if hand is not None and runs[a.layer] == 1 and runs[b.layer] == 1:
+                hand(blocks[b.layer])
 
     def entry_needs(self):
         """For each entry of the plan's order: (cache needs of its mixer, the

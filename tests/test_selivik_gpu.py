@@ -598,3 +598,59 @@ def test_command_line_from_a_configuration_to_tokens(tmp_path, capsys):
     out = capsys.readouterr().out
     generated = [int(t) for t in out.split("Output:\n")[1].splitlines()[0].split(",")]
     assert len(generated) == 5 and generated[0] == top["ids"][0]
+
+
+@pytest.mark.parametrize("heads,dim,rot_dim,vdim,kv_rank,q_rank", [(4, 16, 8, 16, 64, 24), (3, 8, 16, 20, 24, 8), (5, 24, 8, 8, 136, 40),
+                                                                 (16, 32, 32, 32, 256, 96), (8, 32, 64, 16, 512, 64),
+                                                                 (64, 8, 8, 8, 40, 16), (1, 16, 24, 16, 8, 16)])
+def test_tensor_core_latent_attention_with_a_rotated_part_against_the_generic_kernel(heads, dim, rot_dim, vdim, kv_rank, q_rank,
+                                                                                    monkeypatch):
+    """bfloat16: the kernel that takes steps with portions of prompts, with cache rows of a latent and a rotated part
+    (together 32 to 576 entries, also no multiples of 16), against the plain implementation and the generic kernel:
+    whole, cut so that tiles end inside key tiles and pages, decoded, and a portion beside single tokens."""
+    from gibbs_b200.parts import latent_attention
+    cfg = one_layer("latent_attention", lat(heads, dim, rot_dim, vdim, kv_rank, q_rank, 0.3), 64)
+    W = make_weights(cfg, 15)
+    T = 330
+    h = bf(torch.randn(T, 64, generator=gen(16)))
+    want = plain_mixer(cfg, 0, W, h)
+    outs = {}
+    for tc in (True, False):
+        monkeypatch.setattr(latent_attention, "USE_TENSOR_CORES", tc)
+        part = part_of(cfg, 0, W, "bfloat16")
+        hz = PartHarness(part, n_pages=64, page_size=16)
+        for rid, cuts in (("whole", [T]), ("cut", [70, 9, 130, 1, 65, 55]), ("decoded", [T - 30, 1])):
+            outs[(tc, rid)] = hz.run_cut(rid, h, cuts)
+            # (the tensor-core kernel reads the absorbed queries in bfloat16 too: a little more where the latent is short)
+            check_rows(outs[(tc, rid)], want, "bfloat16", what=f"tensor cores {tc}, {rid}", tol=5e-2)
+            hz.close(rid)
+        first = hz.feed_many({"a": h[:200], "b": h[:100]})
+        second = hz.feed_many({"a": h[200:201], "b": h[100:T]})
+        third = hz.feed_many({"a": h[201:T]})
+        outs[(tc, "mixed a")] = torch.cat([first["a"], second["a"], third["a"]], 0)
+        outs[(tc, "mixed b")] = torch.cat([first["b"], second["b"]], 0)
+        check_rows(outs[(tc, "mixed a")], want, "bfloat16", what=f"tensor cores {tc}, mixed a", tol=5e-2)
+        check_rows(outs[(tc, "mixed b")], want, "bfloat16", what=f"tensor cores {tc}, mixed b", tol=5e-2)
+    assert not torch.equal(outs[(True, "whole")], outs[(False, "whole")])       # (two kernels did run)
+    for rid in ("whole", "cut", "mixed a", "mixed b"):
+        assert rel_rows(outs[(True, rid)], outs[(False, rid)]).max() < 5e-2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_norm_taken_by_the_sum_in_front_of_it_changes_nothing(dtype, monkeypatch):
+    """A layer's norm runs inside the kernel that completes the layer in front of it; built without that, the model
+    gives the same logits up to the order in which a row's squares are added."""
+    from gibbs_b200.parts import block
+    cfg, seed = CONFIGS["D"]
+    reqs = {f"r{n}": ids_for(cfg, 300 + n, n) for n in (1, 37, 90)}
+    steps = trace_mixed(reqs, capacity_tokens=256, max_live=3, seed=2)
+    outs = []
+    for fuse in (True, False):
+        monkeypatch.setattr(block, "FUSE_NEXT_NORM", fuse)
+        _, model = build(cfg, seed, dtype)
+        assert (model.blocks[0]._next is not None) == fuse
+        eng = engine_for(model, n_pages=16, max_requests=3, cap=256)
+        assert eng.plan is not None
+        outs.append(run_trace_on_engine(eng, steps))
+    for rid in reqs:
+        check_rows(outs[0][rid], outs[1][rid], dtype, what=rid, tol=2e-5 if dtype == "float32" else TOL[dtype], most=True)
