@@ -83,21 +83,22 @@ struct GemmParams {
   int vec_store;                // 1: out rows are 16-byte aligned (base and row stride)
   int* status;
   // the gated unit of mode OUT_SWIGLU: g' = min(g, limit), u' = clamp(u, -limit, limit) + add, out =
-  // g' * sigmoid(alpha * g') * u'.  SwiGLU is alpha 1, no limit (infinity), add 0.
-  float glu_alpha, glu_limit, glu_add;
+  // g' * sigmoid(alpha * (g' + cubic * g'^3)) * u'.  SwiGLU is alpha 1, no limit (infinity), add 0, cubic 0; the tanh
+  // form of gelu as the gate's function is alpha 2 sqrt(2 / pi), cubic 0.044715 (0.5 (1 + tanh y) = sigmoid(2 y)).
+  float glu_alpha, glu_limit, glu_add, glu_cubic;
 };
 
-__device__ __forceinline__ float glu_exact(float alpha, float limit, float add, float g, float u) {
+__device__ __forceinline__ float glu_exact(float alpha, float limit, float add, float cubic, float g, float u) {
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit) + add;
-  const float sig = 1.0f / (1.0f + expf(-alpha * g));
+  const float sig = 1.0f / (1.0f + expf(-alpha * fmaf(cubic * g, g * g, g)));
   return (g * sig) * u;
 }
 // the same with the fast exponential and division (the result is rounded to bfloat16, which hides both)
 __device__ __forceinline__ float glu_fast(const GemmParams& p, float g, float u) {
   g = fminf(g, p.glu_limit);
   u = fminf(fmaxf(u, -p.glu_limit), p.glu_limit) + p.glu_add;
-  return __fdividef(g, 1.0f + __expf(-p.glu_alpha * g)) * u;
+  return __fdividef(g, 1.0f + __expf(-p.glu_alpha * fmaf(p.glu_cubic * g, g * g, g))) * u;
 }
 
 __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -854,7 +855,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 for (int j = 0; j < 16; ++j)
                   if (c0 + j < hc)
                     ((bf16*)p.out)[(size_t)(m0 + h0 + c0 + j) * p.ldo + (n0 >> 1) + row] =
-                        __float2bfloat16_rn(glu_exact(p.glu_alpha, p.glu_limit, p.glu_add, v[j] + b, ub[(c0 + j) * 64 + row]));
+                        __float2bfloat16_rn(glu_exact(p.glu_alpha, p.glu_limit, p.glu_add, p.glu_cubic, v[j] + b, ub[(c0 + j) * 64 + row]));
               }
             }
           } else if (hc > 0) {
@@ -894,7 +895,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
 // out = epilogue(sum over splits of the partial tiles (+ bias)), in split order.
 __global__ void splitk_reduce_kernel(const float* ws, int splits, const float* __restrict__ bias,
                                      void* __restrict__ out, long long ldo, int mode, int M, int N, float glu_alpha,
-                                     float glu_limit, float glu_add) {
+                                     float glu_limit, float glu_add, float glu_cubic) {
   pdl_trigger();
   pdl_wait();
   const long long total = (long long)M * N;
@@ -914,7 +915,7 @@ __global__ void splitk_reduce_kernel(const float* ws, int splits, const float* _
         g += bias[n];
         u += bias[n + 64];
       }
-      ((bf16*)out)[(size_t)m * ldo + c] = __float2bfloat16_rn(glu_exact(glu_alpha, glu_limit, glu_add, g, u));
+      ((bf16*)out)[(size_t)m * ldo + c] = __float2bfloat16_rn(glu_exact(glu_alpha, glu_limit, glu_add, glu_cubic, g, u));
     } else {
       float acc = 0.f;
       for (int s = 0; s < splits; ++s) acc += ws[(size_t)s * total + (size_t)m * N + c];
@@ -1165,27 +1166,29 @@ GB_API int gb_linear_tc_supported(const void* X, long long ldx, const void* W, l
 // Returns the number of kernels launched, or a negative error code.
 static int linear_tc_impl(const void* X, long long ldx, const void* W, long long ldw, const float* bias, void* out,
                           int mode, long long ldo, int M, int N, int K, float* workspace, int defer, int flags,
-                          int* status, cudaStream_t stream, float glu_alpha, float glu_limit, float glu_add);
+                          int* status, cudaStream_t stream, float glu_alpha, float glu_limit, float glu_add,
+                          float glu_cubic);
 
 GB_API int gb_linear_tc(const void* X, long long ldx, const void* W, long long ldw, const float* bias, void* out,
                         int mode, long long ldo, int M, int N, int K, float* workspace, int defer,
                         int flags, int* status, cudaStream_t stream) {
   return linear_tc_impl(X, ldx, W, ldw, bias, out, mode, ldo, M, N, K, workspace, defer, flags, status, stream, 1.f,
-                        INFINITY, 0.f);
+                        INFINITY, 0.f, 0.f);
 }
 
-// The same with the gated unit of mode 3 given by its constants: out = g' * sigmoid(alpha * g') * (u' + add) with
-// g' = min(g, limit), u' = clamp(u, -limit, limit); limit <= 0 means none.
+// The same with the gated unit of mode 3 given by its constants: out = g' * sigmoid(alpha * (g' + cubic * g'^3)) *
+// (u' + add) with g' = min(g, limit), u' = clamp(u, -limit, limit); limit <= 0 means none.
 GB_API int gb_linear_tc_glu(const void* X, long long ldx, const void* W, long long ldw, const float* bias, void* out,
                             int mode, long long ldo, int M, int N, int K, float* workspace, int defer, int flags,
-                            int* status, cudaStream_t stream, float alpha, float limit, float add) {
+                            int* status, cudaStream_t stream, float alpha, float limit, float add, float cubic) {
   return linear_tc_impl(X, ldx, W, ldw, bias, out, mode, ldo, M, N, K, workspace, defer, flags, status, stream, alpha,
-                        limit > 0.f ? limit : INFINITY, add);
+                        limit > 0.f ? limit : INFINITY, add, cubic);
 }
 
 static int linear_tc_impl(const void* X, long long ldx, const void* W, long long ldw, const float* bias, void* out,
                           int mode, long long ldo, int M, int N, int K, float* workspace, int defer, int flags,
-                          int* status, cudaStream_t stream, float glu_alpha, float glu_limit, float glu_add) {
+                          int* status, cudaStream_t stream, float glu_alpha, float glu_limit, float glu_add,
+                          float glu_cubic) {
   if (M <= 0 || N <= 0) return 0;
   if (!gb_linear_tc_supported(X, ldx, W, ldw, K))
     GB_FAIL(GB_ERR_ARG, "gb_linear_tc: K = %d and the row strides (%lld, %lld) must be multiples of 8 and the bases "
@@ -1234,7 +1237,7 @@ static int linear_tc_impl(const void* X, long long ldx, const void* W, long long
   p.stream_weights = (decode_like && (flags & 1)) ? 1 : 0;   // flags bit 0: evict-first hint for the weights
   p.vec_store = (((uintptr_t)out & 15) == 0 && (ldo * (mode == OUT_BF16 || mode == OUT_SWIGLU ? 2 : 4)) % 16 == 0) ? 1 : 0;
   p.status = status;
-  p.glu_alpha = glu_alpha; p.glu_limit = glu_limit; p.glu_add = glu_add;
+  p.glu_alpha = glu_alpha; p.glu_limit = glu_limit; p.glu_add = glu_add; p.glu_cubic = glu_cubic;
   int rc;
   const long long n_tiles = (long long)gb_div_up(N, BM) * gb_div_up(M, bn);
   if (pairs) {
@@ -1253,7 +1256,7 @@ static int linear_tc_impl(const void* X, long long ldx, const void* W, long long
     const long long work = (long long)M * (mode == OUT_SWIGLU ? N / 2 : N);
     const int blocks = (int)((work + 255) / 256 < 148 * 8 ? (work + 255) / 256 : 148 * 8);
     gb_launch(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, workspace, splits, bias, out, ldo, mode, M, N,
-              p.glu_alpha, p.glu_limit, p.glu_add);
+              p.glu_alpha, p.glu_limit, p.glu_add, p.glu_cubic);
     GB_CHECK_LAUNCH("gb_linear_tc (split-K reduce)");
     return 2;
   }
@@ -1347,7 +1350,7 @@ GB_API int gb_linear_tc_no_alloc(const void* X, long long ldx, const void* W, lo
   p.stream_weights = M <= 64 ? 1 : 0;
   p.vec_store = (((uintptr_t)out & 15) == 0 && (ldo * (mode == OUT_BF16 || mode == OUT_SWIGLU ? 2 : 4)) % 16 == 0) ? 1 : 0;
   p.status = status;
-  p.glu_alpha = 1.f; p.glu_limit = INFINITY; p.glu_add = 0.f;
+  p.glu_alpha = 1.f; p.glu_limit = INFINITY; p.glu_add = 0.f; p.glu_cubic = 0.f;
   int rc;
   switch (bn) {
     case 16: rc = launch<16>(tw, tx, p, stream); break;
@@ -1361,7 +1364,7 @@ GB_API int gb_linear_tc_no_alloc(const void* X, long long ldx, const void* W, lo
     const long long work = (long long)M * (mode == OUT_SWIGLU ? N / 2 : N);
     const int blocks = (int)((work + 255) / 256 < 148 * 8 ? (work + 255) / 256 : 148 * 8);
     gb_launch(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, (const float*)ws, splits, bias, out, ldo, mode,
-              M, N, p.glu_alpha, p.glu_limit, p.glu_add);
+              M, N, p.glu_alpha, p.glu_limit, p.glu_add, p.glu_cubic);
     GB_CHECK_LAUNCH("gb_linear_tc_no_alloc (split-K reduce)");
     return 2;
   }

@@ -37,7 +37,7 @@ typedef int (*LinearSimtFn)(const void*, int, long long, const void*, int, long 
 typedef int (*LinearTcFn)(const void*, long long, const void*, long long, const float*, void*, int, long long, int, int,
                           int, float*, int, int, int*, cudaStream_t);
 typedef int (*LinearTcGluFn)(const void*, long long, const void*, long long, const float*, void*, int, long long, int, int,
-                             int, float*, int, int, int*, cudaStream_t, float, float, float);
+                             int, float*, int, int, int*, cudaStream_t, float, float, float, float);
 typedef int (*LinearTcSplitsFn)(int, int, int);
 typedef int (*ShortConvFn)(const void*, int, long long, const float*, const float*, float*, long long, const int*,
                            const int*, const int*, const int*, void*, int, int, int, int, int, cudaStream_t);
@@ -92,6 +92,13 @@ enum LinearFlag : int { LF_RESIDUAL = 1, LF_PARTIALS_IF_ONE_EACH = 2, LF_PARTIAL
 enum NormFlag : int { NF_LAZY = 1 };      // the product after it may run the norm itself (up to 64 rows)
 constexpr int FIRST_REGISTERED_OP = 64;
 constexpr int MAX_REGISTERED_OPS = 64;
+
+static inline float float_of_bits(long long v) {
+  const unsigned u = (unsigned)v;
+  float f;
+  memcpy(&f, &u, sizeof f);
+  return f;
+}
 
 struct PlanOp {              // 232 bytes; the meaning of a[] per operation is given where it is executed
   int op;
@@ -190,7 +197,8 @@ int run_op(Walk& w, const PlanOp& o, bool force = false) {
       // a0 x, a1 its row stride, a2 W, a3 its row stride, a4 bias, a5 out, a6 its row stride, a7 rows (N or W, a
       // symbol), a8 n, a9 k, a10 kernel (0 tensor cores, 1 FFMA), a11 mode (0 bf16, 1 f32, 2 add into f32, 3 SwiGLU),
       // a12 x dtype, a13 W dtype, a14 out dtype; mode 3 with f0 != 0: the gated unit's constants f0 alpha, f1 limit
-      // (0: none), f2 what is added to u (all zero: SwiGLU)
+      // (0: none), f2 what is added to u (all zero: SwiGLU), a15 the bits of a 32-bit float: the cubic term inside the
+      // gate's sigmoid (0: none)
       const bool glu = a[11] == 3 && o.f[0] != 0.0;
       const int M = (int)val(w, a[7]);
       if (M <= 0) return 0;
@@ -245,7 +253,7 @@ int run_op(Walk& w, const PlanOp& o, bool force = false) {
           PLAN_CALL(w, F_LINEAR_TC_GLU, ((LinearTcGluFn)g_fn[F_LINEAR_TC_GLU])(
               ptr<const void>(w, a[0]), a[1], ptr<const void>(w, a[2]), a[3], bias, ptr<void>(w, a[5]), (int)a[11], a[6],
               M, n, k, splits > 1 ? w.ws : nullptr, 0, w.tc_flags, w.status, w.stream, (float)o.f[0], (float)o.f[1],
-              (float)o.f[2]));
+              (float)o.f[2], float_of_bits(a[15])));
         else
         PLAN_CALL(w, F_LINEAR_TC, ((LinearTcFn)g_fn[F_LINEAR_TC])(
             ptr<const void>(w, a[0]), a[1], ptr<const void>(w, a[2]), a[3], bias, ptr<void>(w, a[5]), (int)a[11], a[6],

@@ -177,8 +177,8 @@ class PlanBuilder:
         float32 residual; partial sums may be left to the next norm) or 'swiglu'.  ``partials``:
         '' | 'one_each' | 'always': when K is split, leave the partial tiles to the next
         operation (a short convolution or q/k kernel that adds them itself).  ``glu`` (mode
-        'swiglu'): (alpha, limit, add) of the gated unit g' sigmoid(alpha g') (u' + add) with
-        g' = min(g, limit), u' = clamp(u, -limit, limit); limit 0: none.  None: SwiGLU."""
+        'swiglu'): (alpha, limit, add[, cubic]) of the gated unit g' sigmoid(alpha (g' + cubic g'^3)) (u' + add)
+        with g' = min(g, limit), u' = clamp(u, -limit, limit); limit 0: none.  None: SwiGLU."""
         n, k = weight.shape
         if x.shape[1] != k or weight.stride(1) != 1 or x.stride(1) != 1:
             raise NotPlannable("a product's operands have contiguous rows of equal length")
@@ -224,8 +224,9 @@ class PlanBuilder:
                              out if isinstance(out, int) else out.data_ptr(),
                              n if isinstance(out, int) else out.stride(0), sym(rows_symbol), n, k, 0 if use_tc else 1,
                              code, ops.dtype_code(x.dtype), ops.dtype_code(weight.dtype),
-                             ops.F32 if isinstance(out, int) else ops.dtype_code(out.dtype)],
-                  [] if glu is None else [float(v) for v in glu], flags=flags, label="linear:" + (role or mode))
+                             ops.F32 if isinstance(out, int) else ops.dtype_code(out.dtype),
+                             0 if glu is None or len(glu) < 4 else int(np.float32(glu[3]).view(np.uint32))],
+                  [] if glu is None else [float(v) for v in glu[:3]], flags=flags, label="linear:" + (role or mode))
         return out
 
     def short_conv(self, bcx: torch.Tensor, taps: torch.Tensor, bias, slot_view, hidden: int, kernel: int):

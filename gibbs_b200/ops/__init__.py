@@ -275,7 +275,7 @@ def linear_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     the kernel splits K, nothing is written to ``out``; the partial sums
     [splits, m, n] are returned instead, for the caller's next kernel to add
     (without the bias).  Otherwise returns ``out``.
-    ``glu`` (with ``swiglu``): (alpha, limit, add) of the gated unit g' sigmoid(alpha g') (u' + add)
+    ``glu`` (with ``swiglu``): (alpha, limit, add[, cubic]) of the gated unit g' sigmoid(alpha (g' + cubic g'^3)) (u' + add)
     with g' = min(g, limit), u' = clamp(u, -limit, limit); limit 0: none."""
     # (this wrapper runs some seventy times a step: its checks are the cheap ones)
     lib = _LIBS.get("tensorcore") or _lib("tensorcore")
@@ -316,7 +316,7 @@ def linear_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     whole = bool(defer and accumulate and splits == 1 and m >= DEFER_WHOLE_ROWS)
     ws = torch.empty((splits, m, n), dtype=torch.float32, device=a.device) if (splits > 1 or whole) else None
     defer = bool(defer and (accumulate or mode == 0) and splits > 1) or whole
-    extra = () if glu is None else tuple(_c_float(float(v)) for v in glu)
+    extra = () if glu is None else tuple(_c_float(float(v)) for v in (tuple(glu) + (0.0,))[:4])
     rc = (lib.gb_linear_tc if glu is None else lib.gb_linear_tc_glu)(
         _c_void(a.data_ptr()), _c_ll(a.stride(0) if m > 1 else max(a.stride(0), k)), _c_void(w.data_ptr()),
         _c_ll(w.stride(0) if n > 1 else max(w.stride(0), k)), _NULL if bias is None else _c_void(bias.data_ptr()),

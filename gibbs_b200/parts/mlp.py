@@ -14,9 +14,14 @@ import torch
 from .. import ops
 from ..ops import hybrid
 from .base import FeedForward, TensorDecl, VECTOR, register_part
+from .linear import can_fuse_swiglu, interleave_gate_up
 from .runner import BranchPart, Runner
 
 ACTIVATIONS = {"gelu": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+# act(g) = g * sigmoid(alpha * (g + cubic * g^3)) for the functions that have this form: (alpha, cubic).  The tanh form
+# of gelu has it because 0.5 (1 + tanh y) = sigmoid(2 y), with y = sqrt(2 / pi) (g + 0.044715 g^3).
+SIGMOID_FORMS = {"silu": (1.0, 0.0), "gelu_tanh": (1.5957691216057308, 0.044715)}
+FUSE_GATED_UNIT = True             # (the tests switch it off to compare the two ways)
 
 
 class DenseMLP(BranchPart, FeedForward):
@@ -70,17 +75,26 @@ class GatedMLP(BranchPart, FeedForward):
         self.act = ACTIVATIONS[act]
         if tensors["gate"].dtype != tensors["up"].dtype:
             raise ValueError("gate and up projections are stored in different dtypes")
-        # one product for [gate rows | up rows]
-        self.gate_up = torch.cat([tensors["gate"], tensors["up"]], 0).contiguous()
+        # one product for gate and up; in bfloat16, for a function of the sigmoid form, its epilogue applies the unit
+        # (gate and up rows then alternate in blocks of 64, as for SwiGLU)
+        self.fused = FUSE_GATED_UNIT and act in SIGMOID_FORMS and can_fuse_swiglu(tensors["gate"], rt)
+        join = interleave_gate_up if self.fused else (lambda g, u: torch.cat([g, u], 0))
+        self.gate_up = join(tensors["gate"], tensors["up"]).contiguous()
+        self.form = SIGMOID_FORMS.get(act)
         self.down = tensors["down"].contiguous()
 
     def kernel_libraries(self):
         return tuple(set(ops.linear_libraries(self.gate_up.dtype, self.rt.dtype)) | {"core", hybrid.LIBRARY})
 
     def run(self, rn: Runner, h, out, caches=None, accumulate: bool = False):
+        act = rn.buffer("gmlp_act", self.inner)
+        if self.fused:
+            alpha, cubic = self.form
+            rn.glu_linear(h, self.gate_up, act, (alpha, 0.0, 0.0, cubic), role="mlp_gate_up")
+            (rn.add_linear if accumulate else rn.linear)(act, self.down, None, out, role="mlp_down")
+            return
         gu = rn.buffer("gmlp_gate_up", 2 * self.inner, torch.float32)
         rn.linear(h, self.gate_up, None, gu, role="mlp_gate_up")
-        act = rn.buffer("gmlp_act", self.inner)
         rn.op("act_rows", [gu.data_ptr(), gu.stride(0), act.data_ptr(), ops.dtype_code(act.dtype), act.stride(0), rn.N,
                            self.inner, self.act, 1], label="act_rows:gated")
         (rn.add_linear if accumulate else rn.linear)(act, self.down, None, out, role="mlp_down")

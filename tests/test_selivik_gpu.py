@@ -654,3 +654,27 @@ def test_the_norm_taken_by_the_sum_in_front_of_it_changes_nothing(dtype, monkeyp
         outs.append(run_trace_on_engine(eng, steps))
     for rid in reqs:
         check_rows(outs[0][rid], outs[1][rid], dtype, what=rid, tol=2e-5 if dtype == "float32" else TOL[dtype], most=True)
+
+
+@pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
+@pytest.mark.parametrize("d,ff,rows", [(128, 256, 70), (96, 128, 5), (320, 64, 300), (64, 1024, 33)])
+def test_gated_unit_in_the_epilogue_of_its_product_against_the_kernel_of_its_own(d, ff, rows, act, monkeypatch):
+    """bfloat16, widths that are multiples of 64: gate and up are one tensor-core product whose epilogue applies
+    act(g) * u in the form g * sigmoid(alpha * (g + cubic * g^3)); against the 32-bit product followed by the
+    activation kernel (the named function itself), and against float64."""
+    from gibbs_b200.parts import mlp
+    g = gen(31)
+    W = {"gate": bf(torch.randn(ff, d, generator=g) * (2.0 / d ** 0.5)), "up": bf(torch.randn(ff, d, generator=g) / d ** 0.5),
+         "down": bf(torch.randn(d, ff, generator=g) / ff ** 0.5)}
+    h = bf(torch.randn(rows, d, generator=g) * 1.5)
+    z = h.double() @ W["gate"].double().T
+    a = plain.gelu_tanh(z) if act == "gelu_tanh" else z * torch.sigmoid(z)
+    want = (a * (h.double() @ W["up"].double().T)) @ W["down"].double().T
+    outs = {}
+    for fuse in (True, False):
+        monkeypatch.setattr(mlp, "FUSE_GATED_UNIT", fuse)
+        part = make_part("feed_forward", "gated_mlp", {"hidden": d, "inner": ff, "act": act}, W, torch.bfloat16)
+        assert part.fused == fuse
+        outs[fuse] = PartHarness(part).feed("r", h)
+        check_rows(outs[fuse], want, "bfloat16", what=f"fused {fuse}", tol=1.5e-2)
+    assert rel_rows(outs[True], outs[False]).max() < 1e-2
