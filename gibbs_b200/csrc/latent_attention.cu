@@ -398,7 +398,8 @@ bool gb_latent_attention_tc_takes(int n, int R, int H, int r, int dr, int window
 int gb_latent_attention_tc_launch(const float* qp, const bf16* pages, const int* block_table, int bt_stride, int page_size,
                                   int n_pages, const int* tok_req, const int* tok_pos, const int* q_start,
                                   const float* gate, long long ld_gate, float* out, long long ldo, int n, int R, int H, int r,
-                                  int dr, float scale, const float* sink, int* status, cudaStream_t stream);
+                                  int dr, float scale, const float* sink, float* ws, long long ws_rows, int* status,
+                                  cudaStream_t stream);
 
 // How the visible keys of a launch are cut into chunks of whole key tiles: (chunks, keys per chunk).
 // Few tokens (decoding) get many chunks, so that the GPU is occupied; a launch with enough (token, head
@@ -423,7 +424,8 @@ GB_API int gb_latent_attention_chunks(int n, int H, int window, int max_ctx, int
   return gb_div_up(span, chunk);
 }
 // Rows of (latent size + 2) floats a launch's partial results may need, whatever its sizes.
-GB_API int gb_latent_attention_workspace_rows() { return LA_HB * 2 * (592 + 592); }
+// (also: two partial results a row for a prompt of up to 2,048 tokens and 16 heads on the tensor-core kernel)
+GB_API int gb_latent_attention_workspace_rows() { return 65536 > LA_HB * 2 * (592 + 592) ? 65536 : LA_HB * 2 * (592 + 592); }
 
 // a0 fused rows [q heads (plain | rotated) | ... ] (f32), a1 their stride, a2 column of [latent | rotated key],
 // a3 gain of the latent's norm [r], a4 inv_freq [rot_dims / 2], a5 rot_dims, a6 token -> request, a7 token ->
@@ -495,13 +497,19 @@ GB_OP(gb_op_latent_attention) {
   if (a[22] &&
       gb_latent_attention_tc_takes(n, (int)a[21], H, r, dr, (int)a[17], a[2] == GB_BF16, op_ptr<const void>(a[1]),
                                    op_ptr<const void>(a[0]), op_ptr<const void>(a[11]), a[12])) {
-    if (gb_latent_attention_tc_launch(op_ptr<const float>(a[0]), op_ptr<const bf16>(a[1]), op_ptr<const int>(a[3]), (int)a[4],
-                                      (int)a[5], (int)a[6], op_ptr<const int>(a[7]), op_ptr<const int>(a[8]),
-                                      op_ptr<const int>(a[22]), op_ptr<const float>(a[9]), a[10],
-                                      op_ptr<float>(a[11]), a[12], n, (int)a[21], H, r, dr, (float)f[0],
-                                      op_ptr<const float>(a[20]), ctx->status, ctx->stream) == 0) {
+    const int parts = gb_latent_attention_tc_launch(
+        op_ptr<const float>(a[0]), op_ptr<const bf16>(a[1]), op_ptr<const int>(a[3]), (int)a[4], (int)a[5], (int)a[6],
+        op_ptr<const int>(a[7]), op_ptr<const int>(a[8]), op_ptr<const int>(a[22]), op_ptr<const float>(a[9]), a[10],
+        op_ptr<float>(a[11]), a[12], n, (int)a[21], H, r, dr, (float)f[0], op_ptr<const float>(a[20]), op_ptr<float>(a[19]),
+        gb_latent_attention_workspace_rows(), ctx->status, ctx->stream);
+    if (parts >= 1) {
       GB_CHECK_LAUNCH("latent_attention (tensor cores)");
-      return 1;
+      if (parts == 1) return 1;
+      gb_launch(latent_attention_merge_kernel, dim3(gb_div_up((long long)n * H, 4)), dim3(128), 0, ctx->stream,
+                op_ptr<const float>(a[19]), parts, op_ptr<const float>(a[9]), a[10], op_ptr<float>(a[11]), a[12], n, H, r,
+                op_ptr<const float>(a[20]));
+      GB_CHECK_LAUNCH("latent_attention_merge");
+      return 2;
     }
   }
   if (r > 512) GB_FAIL(GB_ERR_ARG, "latent_attention: latent size %d (at most 512)", r);

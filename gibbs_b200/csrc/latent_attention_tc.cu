@@ -13,7 +13,9 @@
 //  the block table into two buffers.  mma.sync.m16n8k16, bfloat16 operands, 32-bit accumulators; the softmax (base
 //  2, running maximum and sum per row) is 32-bit, and its weights enter the second product as TWO bfloat16 terms
 //  (p = hi + lo), so 16 bits of every weight count.  A learned sink per head joins the denominator at the end; an
-//  optional gate multiplies the result.  Causal, no window: what has one runs on the generic kernel, as do 32-bit
+//  optional gate multiplies the result.  With `splits` 2 (a step of few tiles: one long prompt) the key tiles of
+//  every row tile are cut in two halves for two CTAs, which leave (maximum, sum, weighted sum) per row for the merge
+//  kernel of latent_attention.cu, and the row tiles with the most keys are launched first.  Causal, no window: what has one runs on the generic kernel, as do 32-bit
 //  pages and steps of single tokens.  Rows in shared memory lie `stride` entries apart: the row's length rounded up
 //  to 16, plus 8 (an odd number of 16-byte pieces, so that ldmatrix meets no bank twice).
 #include "hybrid.cuh"
@@ -21,6 +23,9 @@
 namespace {
 
 enum { LTC_BAD_PAGE_READ = 2 };
+#ifndef LTC_SPLIT_KEYS
+#define LTC_SPLIT_KEYS 1
+#endif
 constexpr int LTC_ROWS = 64, LTC_KEYS = 64;
 
 __device__ __forceinline__ void ltc_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
@@ -69,6 +74,8 @@ struct LtcParams {
   long long ldo;
   int H, r, tpt;
   int dk, stride;           // entries of a cached row (r + rotated part); entries between rows in shared memory
+  int splits;               // 1, or 2: blockIdx.z takes one half of a row tile's key tiles and writes partial results
+  float* ws;                // [tokens * heads][splits][r + 2] partial results (splits > 1)
   float scale_log2;
   const float* sink;
   int* status;
@@ -87,7 +94,8 @@ __global__ void __launch_bounds__(RP > 256 ? 256 : 128, 1) latent_attention_tc_k
   const int g = lane >> 2, t4 = lane & 3;
   const int req = blockIdx.y;
   const int first = p.q_start[req], len = (req + 1 < p.R ? p.q_start[req + 1] : p.n) - first;
-  const int tok0 = blockIdx.x * p.tpt;
+  // (the row tiles with the most keys go first: where the grid is more than a wave, the short ones fill the end)
+  const int tok0 = (int)(gridDim.x - 1 - blockIdx.x) * p.tpt;
   if (tok0 >= len) return;
   const int ntok = min(p.tpt, len - tok0), H = p.H, r = p.r;
   const int rows_live = ntok * H;
@@ -115,8 +123,12 @@ __global__ void __launch_bounds__(RP > 256 ? 256 : 128, 1) latent_attention_tc_k
     }
     ltc_commit();
   };
+  const int tiles = kmax / LTC_KEYS + 1;
+  const int half_tiles = (tiles + 1) >> 1;
+  const int kt_begin = p.splits > 1 ? (int)blockIdx.z * half_tiles : 0;
+  const int kt_end = p.splits > 1 ? min(tiles, kt_begin + half_tiles) : tiles;
   pdl_wait();
-  stage(0, 0);
+  if (kt_begin < kt_end) stage(kt_begin, 0);
   {
     // this tile's queries: rows_live consecutive rows of dk floats, rounded to bfloat16
     const float* src = p.qp + (size_t)t_first * H * dk;
@@ -144,10 +156,10 @@ __global__ void __launch_bounds__(RP > 256 ? 256 : 128, 1) latent_attention_tc_k
   const int ksteps = (dk + 15) >> 4;                       // k-steps of the first product that hold anything
   const int npairs = min(OC / 16, max(0, (r - wn * OC + 15) >> 4));   // pairs of 8 output columns likewise
 
-  const int tiles = kmax / LTC_KEYS + 1;
-  for (int kt = 0; kt < tiles; ++kt) {
-    const int b = kt & 1;
-    if (kt + 1 < tiles) {
+  if (kt_begin >= kt_end) __syncthreads();                 // (the queries and zeros are written; no key tile follows)
+  for (int kt = kt_begin; kt < kt_end; ++kt) {
+    const int b = (kt - kt_begin) & 1;
+    if (kt + 1 < kt_end) {
       stage(kt + 1, b ^ 1);
       ltc_wait<1>();
     } else {
@@ -254,6 +266,23 @@ __global__ void __launch_bounds__(RP > 256 ? 256 : 128, 1) latent_attention_tc_k
     const int tl = half ? tl_b : tl_a, h = half ? h_b : h_a;
     const float m = half ? m_b : m_a, l = half ? l_b : l_a;
     const size_t t = (size_t)t_first + tl;
+    if (p.splits > 1) {
+      // this half's partial result: maximum (natural units), sum of weights, weighted sum, for the merge kernel
+      float* w = p.ws + ((t * H + h) * p.splits + blockIdx.z) * (size_t)(r + 2);
+      if (wn == 0 && t4 == 0) {
+        w[0] = m * 0.6931471805599453f;                    // (-inf stays -inf: a half without keys)
+        w[1] = l;
+      }
+#pragma unroll
+      for (int j = 0; j < OC / 8; ++j) {
+        const int col = wn * OC + 8 * j + 2 * t4;
+        if (col < r) {
+          w[2 + col] = o[j][2 * half];
+          w[2 + col + 1] = o[j][2 * half + 1];
+        }
+      }
+      continue;
+    }
     float f = 1.f / l;
     if (p.sink) {
       // a learned score without a key or a value: only the denominator knows it
@@ -280,7 +309,7 @@ template <int RP> int ltc_launch(const LtcParams& p, int tiles, int R, cudaStrea
       return -1;
     allowed = smem;
   }
-  gb_launch(latent_attention_tc_kernel<RP>, dim3(tiles, R), dim3(128 * NSPLIT), smem, stream, p);
+  gb_launch(latent_attention_tc_kernel<RP>, dim3(tiles, R, p.splits), dim3(128 * NSPLIT), smem, stream, p);
   return 0;
 }
 
@@ -404,12 +433,16 @@ bool gb_latent_attention_tc_takes(int n, int R, int H, int r, int dr, int window
          ((uintptr_t)out & 7) == 0 && ldo % 2 == 0;
 }
 
-// Returns 0 after the launch, -1 when the kernel's shared memory could not be had.
+// Returns the number of partial results a row has after the launch (1: `out` is final; 2: the caller merges the
+// workspace's partial results), or -1 when the kernel's shared memory could not be had.  The key tiles are split in
+// two when the launch has few CTAs (a long prompt of one or two requests) and the workspace has the rows.
 int gb_latent_attention_tc_launch(const float* qp, const bf16* pages, const int* block_table, int bt_stride, int page_size,
                                   int n_pages, const int* tok_req, const int* tok_pos, const int* q_start,
                                   const float* gate, long long ld_gate, float* out, long long ldo, int n, int R, int H, int r,
-                                  int dr, float scale, const float* sink, int* status, cudaStream_t stream) {
+                                  int dr, float scale, const float* sink, float* ws, long long ws_rows, int* status,
+                                  cudaStream_t stream) {
   LtcParams p;
+  p.ws = ws;
   p.dk = r + dr;
   p.stride = 16 * ((p.dk + 15) / 16) + 8;
   p.qp = qp; p.pages = pages; p.block_table = block_table; p.bt_stride = bt_stride; p.page_size = page_size;
@@ -417,8 +450,16 @@ int gb_latent_attention_tc_launch(const float* qp, const bf16* pages, const int*
   p.ld_gate = ld_gate; p.out = out; p.ldo = ldo; p.H = H; p.r = r; p.tpt = LTC_ROWS / H;
   p.scale_log2 = scale * 1.4426950408889634f; p.sink = sink; p.status = status;
   const int tiles = gb_div_up(n, p.tpt);                   // (no request has more tokens than the step)
-  if (r <= 64) return ltc_launch<64>(p, tiles, R, stream);
-  if (r <= 128) return ltc_launch<128>(p, tiles, R, stream);
-  if (r <= 256) return ltc_launch<256>(p, tiles, R, stream);
-  return ltc_launch<512>(p, tiles, R, stream);
+  // (which way a launch goes depends on its numbers of tokens, requests and heads only)
+  // two halves where the row tiles alone do not fill the GPU's resident CTAs (two an SM by registers, fewer where three
+  // tiles of rows need more than half of an SM's shared memory)
+  const size_t smem = sizeof(bf16) * 3 * LTC_ROWS * (size_t)p.stride;
+  const int resident = 148 * (smem <= 113 * 1024 ? 2 : 1);
+  p.splits = (LTC_SPLIT_KEYS && ws != nullptr && (long long)tiles * R <= resident && n >= 512 * R && 2LL * n * H <= ws_rows) ? 2 : 1;
+  int rc;
+  if (r <= 64) rc = ltc_launch<64>(p, tiles, R, stream);
+  else if (r <= 128) rc = ltc_launch<128>(p, tiles, R, stream);
+  else if (r <= 256) rc = ltc_launch<256>(p, tiles, R, stream);
+  else rc = ltc_launch<512>(p, tiles, R, stream);
+  return rc < 0 ? rc : p.splits;
 }

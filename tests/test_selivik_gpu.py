@@ -678,3 +678,21 @@ def test_gated_unit_in_the_epilogue_of_its_product_against_the_kernel_of_its_own
         outs[fuse] = PartHarness(part).feed("r", h)
         check_rows(outs[fuse], want, "bfloat16", what=f"fused {fuse}", tol=1.5e-2)
     assert rel_rows(outs[True], outs[False]).max() < 1e-2
+
+
+@pytest.mark.parametrize("heads,dim,rot_dim,vdim,kv_rank,q_rank", [(4, 16, 8, 16, 64, 24), (16, 8, 16, 8, 40, 16), (2, 16, 8, 16, 264, 16),
+                                                                 (8, 16, 32, 16, 288, 32)])
+def test_a_long_prompt_whose_key_tiles_two_blocks_share(heads, dim, rot_dim, vdim, kv_rank, q_rank):
+    """bfloat16: a step of one long portion has few tiles of rows, so every tile's key tiles are cut in two halves
+    whose partial results a second kernel merges; a row may see nothing of the second half.  Whole (700 tokens) and
+    as a portion of 600 behind 100 tokens, against the plain implementation."""
+    cfg = one_layer("latent_attention", lat(heads, dim, rot_dim, vdim, kv_rank, q_rank, 0.3), 64)
+    W = make_weights(cfg, 17)
+    T = 700
+    h = bf(torch.randn(T, 64, generator=gen(18)))
+    want = plain_mixer(cfg, 0, W, h)
+    part = part_of(cfg, 0, W, "bfloat16")
+    hz = PartHarness(part, n_pages=96, page_size=16)
+    for rid, cuts in (("whole", [T]), ("behind", [100, 600])):
+        check_rows(hz.run_cut(rid, h, cuts), want, "bfloat16", what=rid, tol=5e-2)
+        hz.close(rid)
