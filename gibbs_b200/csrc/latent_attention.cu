@@ -262,44 +262,72 @@ latent_attention_kernel(const float* qp, const TC* pages, const int* block_table
     __syncthreads();
     if (hw >= H) continue;
     const int n_keys = min(LA_KT, k_end - k0 + 1);
-    for (int j = 0; j < n_keys; ++j) {
-      const float* row = ks + j * Dk;
-      float kl[RL], kr[LA_RR];
+    // Keys are taken KG at a time: their rows are read and their scores' partial products and warp sums are worked
+    // out side by side (independent chains that hide one another's latencies: a step of a few tokens is bound by
+    // them), then the softmax takes the keys one after the other.  Every number is computed by the same operations
+    // in the same order as with one key at a time.
+    constexpr int KG = RL <= 8 ? 4 : 1;                     // (latents beyond 256 entries fill the registers: one key at a time)
+    for (int j0 = 0; j0 < n_keys; j0 += KG) {
+      float kl[KG][RL], kr[KG][LA_RR], sc[KG][LA_HW];
 #pragma unroll
-      for (int i = 0; i < RL; ++i) {
-        const int d = lane + 32 * i;
-        kl[i] = d < r ? row[d] : 0.f;
-      }
-#pragma unroll
-      for (int i = 0; i < LA_RR; ++i) {
-        const int d = lane + 32 * i;
-        kr[i] = d < dr ? row[r + d] : 0.f;
-      }
-#pragma unroll
-      for (int hh = 0; hh < LA_HW; ++hh) {
-        float p0 = 0.f, p1 = 0.f;                          // two chains; added in a fixed order
+      for (int u = 0; u < KG; ++u) {
+        const float* row = ks + min(j0 + u, n_keys - 1) * Dk;      // (a key beyond the tile's last: read again, not used)
 #pragma unroll
         for (int i = 0; i < RL; ++i) {
-          if (i & 1) p1 = fmaf(ql[hh][i], kl[i], p1);
-          else p0 = fmaf(ql[hh][i], kl[i], p0);
+          const int d = lane + 32 * i;
+          kl[u][i] = d < r ? row[d] : 0.f;
         }
 #pragma unroll
         for (int i = 0; i < LA_RR; ++i) {
-          if (i & 1) p1 = fmaf(qr[hh][i], kr[i], p1);
-          else p0 = fmaf(qr[hh][i], kr[i], p0);
+          const int d = lane + 32 * i;
+          kr[u][i] = d < dr ? row[r + d] : 0.f;
         }
-        const float sc = warp_sum(p0 + p1) * scale;       // every lane gets the same sum
-        if (sc > m[hh]) {                                  // (the whole warp together)
-          const float corr = la_exp<TC>(m[hh] - sc);       // 0 for the first key: m = -inf
-          l[hh] *= corr;
+      }
 #pragma unroll
-          for (int i = 0; i < RL; ++i) acc[hh][i] *= corr;
-          m[hh] = sc;
+      for (int u = 0; u < KG; ++u) {
+#pragma unroll
+        for (int hh = 0; hh < LA_HW; ++hh) {
+          float p0 = 0.f, p1 = 0.f;                          // two chains; added in a fixed order
+#pragma unroll
+          for (int i = 0; i < RL; ++i) {
+            if (i & 1) p1 = fmaf(ql[hh][i], kl[u][i], p1);
+            else p0 = fmaf(ql[hh][i], kl[u][i], p0);
+          }
+#pragma unroll
+          for (int i = 0; i < LA_RR; ++i) {
+            if (i & 1) p1 = fmaf(qr[hh][i], kr[u][i], p1);
+            else p0 = fmaf(qr[hh][i], kr[u][i], p0);
+          }
+          sc[u][hh] = p0 + p1;
         }
-        const float p = la_exp<TC>(sc - m[hh]);
-        l[hh] += p;
+      }
+      // the warp sums of all scores, step by step (every lane gets the same sums)
 #pragma unroll
-        for (int i = 0; i < RL; ++i) acc[hh][i] = fmaf(p, kl[i], acc[hh][i]);
+      for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int u = 0; u < KG; ++u) {
+#pragma unroll
+          for (int hh = 0; hh < LA_HW; ++hh) sc[u][hh] += __shfl_xor_sync(0xffffffffu, sc[u][hh], o);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < KG; ++u) {
+        if (j0 + u >= n_keys) break;                         // (the whole warp together)
+#pragma unroll
+        for (int hh = 0; hh < LA_HW; ++hh) {
+          const float s1 = sc[u][hh] * scale;
+          if (s1 > m[hh]) {                                  // (the whole warp together)
+            const float corr = la_exp<TC>(m[hh] - s1);       // 0 for the first key: m = -inf
+            l[hh] *= corr;
+#pragma unroll
+            for (int i = 0; i < RL; ++i) acc[hh][i] *= corr;
+            m[hh] = s1;
+          }
+          const float p = la_exp<TC>(s1 - m[hh]);
+          l[hh] += p;
+#pragma unroll
+          for (int i = 0; i < RL; ++i) acc[hh][i] = fmaf(p, kl[u][i], acc[hh][i]);
+        }
       }
     }
   }

@@ -103,13 +103,13 @@ class Rows:
         self.token_ids = self.tok_req = self.tok_pos = self.q_start = self.q_len = self.start_pos = self.want_rows = z
 
 
-@pytest.mark.parametrize("d", [44, 320, 1536, 5000])
+@pytest.mark.parametrize("d", [44, 46, 320, 1536, 5000])
 @pytest.mark.parametrize("branches", [("mixer",), ("mixer", "ffn")])
 def test_scaled_sum_of_branches_and_the_norm_behind_it(d, branches):
     from gibbs_b200.parts.base import Runtime
     from gibbs_b200.parts.runner import Eager
     g = gen(2)
-    n, mult = 7, 0.37
+    n, mult = (7 if d == 1536 else 70), 0.37               # (64 rows and more of up to 1,024 entries: a warp a row)
     scales = {b: bf(1.0 + 0.4 * torch.randn(d, generator=g)) for b in branches}
     x, ys = torch.randn(n, d, generator=g), [torch.randn(n, d, generator=g) for _ in branches]
     part = make_part("branch_sum", "scaled_sum", {"dim": d, "mult": mult, "branches": branches}, scales)
