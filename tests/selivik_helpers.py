@@ -85,7 +85,7 @@ CFG_D = {
     "architecture": "Selivik", "vocab": 211, "width": 128, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
     "embedding": {"scale": 11.0},
     "layers": [
-        layer("attention", att(4, 2, 64, 64, 0.125, window=100, keep_first=20, softcap=30.0, rot=(500000.0, 64), factor=8.0),
+        layer("attention", att(8, 2, 64, 64, 0.11, window=100, keep_first=20, softcap=25.0, rot=(250000.0, 64), factor=4.0),
               moe(8, 2, 64)),
         layer("latent_attention", lat(4, 64, 32, 64, 128, 96, 0.1), dense(256)),
         layer("attention", att(2, 1, 128, 32, 0.09, window=48, keep_first=4, softcap=20.0, rot=(500.0, 32)), moe(4, 2, 128)),

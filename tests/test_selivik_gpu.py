@@ -82,7 +82,7 @@ def layers_of(kind):
 # ---------------------------------------------------------------------------
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("d", [44, 64, 320, 2100])
+@pytest.mark.parametrize("d", [44, 64, 336, 2100])
 def test_norm_whose_weight_is_stored_around_zero(d, dtype):
     g = gen(1)
     w = bf(torch.randn(d, generator=g) * 0.2)
@@ -103,7 +103,7 @@ class Rows:
         self.token_ids = self.tok_req = self.tok_pos = self.q_start = self.q_len = self.start_pos = self.want_rows = z
 
 
-@pytest.mark.parametrize("d", [44, 46, 320, 1536, 5000])
+@pytest.mark.parametrize("d", [44, 46, 336, 1536, 5000])
 @pytest.mark.parametrize("branches", [("mixer",), ("mixer", "ffn")])
 def test_scaled_sum_of_branches_and_the_norm_behind_it(d, branches):
     from gibbs_b200.parts.base import Runtime
@@ -172,13 +172,13 @@ def _pointed_attention(window, keep_first, T, hot, query, vdim=8, seed=7):
 
 POINTED = [
     # window, kept first, tokens, hot key, query
-    (40, 6, 120, 60, 99),         # the last position inside the window
-    (40, 6, 120, 59, 99),         # the first one outside
-    (40, 6, 120, 5, 99),          # the last kept first position
-    (40, 6, 120, 6, 99),          # the first one that is not kept
-    (40, 6, 120, 0, 99),          # the first token of the sequence
-    (40, 0, 120, 0, 99),          # ... which a window without kept positions does not see
-    (40, 6, 120, 0, 30),          # a query whose window still reaches the start
+    (44, 5, 120, 56, 99),         # the last position inside the window
+    (44, 5, 120, 55, 99),         # the first one outside
+    (44, 5, 120, 4, 99),          # the last kept first position
+    (44, 5, 120, 5, 99),          # the first one that is not kept
+    (44, 5, 120, 0, 99),          # the first token of the sequence
+    (44, 0, 120, 0, 99),          # ... which a window without kept positions does not see
+    (44, 5, 120, 0, 30),          # a query whose window still reaches the start
     (16, 17, 120, 16, 95),        # kept positions beyond a page: the first row of the second page
     (16, 17, 120, 17, 95),
     (16, 16, 120, 80, 95),        # a window of one page
@@ -657,7 +657,7 @@ def test_the_norm_taken_by_the_sum_in_front_of_it_changes_nothing(dtype, monkeyp
 
 
 @pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
-@pytest.mark.parametrize("d,ff,rows", [(128, 256, 70), (96, 128, 5), (320, 64, 300), (64, 1024, 33)])
+@pytest.mark.parametrize("d,ff,rows", [(128, 256, 70), (96, 128, 5), (336, 64, 300), (64, 1024, 33)])
 def test_gated_unit_in_the_epilogue_of_its_product_against_the_kernel_of_its_own(d, ff, rows, act, monkeypatch):
     """bfloat16, widths that are multiples of 64: gate and up are one tensor-core product whose epilogue applies
     act(g) * u in the form g * sigmoid(alpha * (g + cubic * g^3)); against the 32-bit product followed by the
